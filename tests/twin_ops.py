@@ -113,14 +113,22 @@ class TwinOps:
 
     # -- the kernels of the stream norm, the linear-attention mixer, the two-map attention and the routed
     # feed-forward (formulas restated from the kernels' own headers) ------------------------------------------
-    def rmsnorm_stream(self, out, stream, add1, add2, weight, eps, first=False):
+    def rmsnorm_stream(self, out, stream, add1, add2, weight, eps, first=False, alpha=1.0, row=None, norm_bias=None):
         total = torch.zeros_like(stream) if first else stream.clone()
         for a in (add1, add2):
             if a is not None:
-                total = total + a.float()
+                total = total + alpha * a.float()
+        if row is not None:
+            total = total + row.float()
         stream.copy_(total)
-        if out is not None:
-            out.copy_((total / torch.sqrt(total.pow(2).mean(-1, keepdim=True) + eps) * weight.float()).to(out.dtype))
+        if out is None:
+            return
+        if norm_bias is not None:
+            dev = total - total.mean(-1, keepdim=True)
+            y = dev / torch.sqrt(dev.pow(2).mean(-1, keepdim=True) + eps) * weight.float() + norm_bias.float()
+        else:
+            y = total / torch.sqrt(total.pow(2).mean(-1, keepdim=True) + eps) * weight.float()
+        out.copy_(y.to(out.dtype))
 
     def gated_rmsnorm(self, out, x, gate, weight, eps):
         y = x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + eps) * weight.float()
@@ -181,15 +189,15 @@ class TwinOps:
                 o = o / torch.sqrt(o.pow(2).mean(-1, keepdim=True) + eps) * out_scale
                 out[qs:qe, h * V:(h + 1) * V] = o.to(out.dtype)
 
-    def router_topk(self, idx, weights, x, w_router, softmax, renormalize):
+    def router_topk(self, idx, weights, x, w_router, softmax, renormalize, correction=None):
         z = F.linear(x.float(), w_router.float())
         scores = torch.softmax(z, -1) if softmax else torch.sigmoid(z)
-        best = z.topk(idx.shape[1], dim=-1)
+        best = (z if correction is None else scores + correction.float()).topk(idx.shape[1], dim=-1)
         idx.copy_(best.indices.to(torch.int32))
         w = scores.gather(1, best.indices)
         weights.copy_(w / w.sum(-1, keepdim=True) if renormalize else w)
 
-    def moe_align(self, idx, E):
+    def moe_align(self, idx, E, with_tiles=None):
         flat = idx.reshape(-1).long()
         order = torch.sort(flat, stable=True).indices.to(torch.int32)
         place = torch.empty_like(order)
@@ -226,8 +234,11 @@ class TwinOps:
             rows = rows * row_scale.reshape(-1)[pairs][:, None]
         xs.copy_(rows.to(xs.dtype))
 
-    def moe_combine(self, out, y, place, pair_weights, top):
+    def moe_combine(self, out, y, place, pair_weights, top, x=None, pass_from=None):
         rows = y[place.long()].view(out.shape[0], top, -1)
+        if x is not None:
+            own = (place.long() >= int(pass_from)).view(out.shape[0], top, 1)
+            rows = torch.where(own, x.float()[:, None, :], rows)
         if pair_weights is not None:
             rows = rows * pair_weights.view(out.shape[0], top, 1)
         acc = torch.zeros(out.shape, dtype=torch.float32)
@@ -391,7 +402,36 @@ def _batched_linear(self, out, x, w):
     out.copy_(torch.einsum("thk,hnk->thn", x.float(), w.float()).to(out.dtype))
 
 
-def _attention_biased(self, out, q, k_cache, v_cache, block_tables, step, KVH, page_size, scale, softcap, slopes, window):
+def _rope_headnorm_write(self, proj, k_off, v_off, positions, freq, rot_dims, norm_eps, k_cache, v_cache, slots, H, G, D, V,
+                         page_size):
+    T = proj.shape[0]
+    q = proj[:, :H * D].float().view(T, H, D)
+    k = proj[:, k_off:k_off + G * D].float().view(T, G, D)
+
+    def turn(x):
+        if rot_dims:
+            half = rot_dims // 2
+            a = positions.float()[:, None] * freq.float()[None, :]
+            c, s = torch.cos(a)[:, None, :], torch.sin(a)[:, None, :]
+            u, v = x[..., :half], x[..., half:rot_dims]
+            x = torch.cat([u * c - v * s, v * c + u * s, x[..., rot_dims:]], -1)
+        if norm_eps is not None:
+            x = x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + norm_eps)
+        return x
+
+    proj[:, :H * D] = turn(q).reshape(T, H * D).to(proj.dtype)
+    if slots is None:
+        return
+    k = turn(k).to(proj.dtype)
+    v = proj[:, v_off:v_off + G * V].view(T, G, V)
+    for t, slot in enumerate(slots.tolist()):
+        if slot >= 0:
+            k_cache[slot // page_size, :, slot % page_size] = k[t]
+            v_cache[slot // page_size, :, slot % page_size] = v[t]
+
+
+def _attention_biased(self, out, q, k_cache, v_cache, block_tables, step, KVH, page_size, scale, softcap, slopes, window,
+                      chunk=None, sinks=None):
     T, H, Dk = q.shape
     Dv = out.shape[2]
     G = H // KVH
@@ -414,6 +454,8 @@ def _attention_biased(self, out, q, k_cache, v_cache, block_tables, step, KVH, p
         ok = j <= i
         if window:
             ok = ok & (j > i - window)
+        if chunk:
+            ok = ok & (j >= i // chunk * chunk)
         vv = torch.where(ok.any(0)[:, None, None], vv, torch.zeros_like(vv))      # pages a window gave back
         kk = torch.where(ok.any(0)[:, None, None], kk, torch.zeros_like(kk))
         for h in range(H):
@@ -422,7 +464,10 @@ def _attention_biased(self, out, q, k_cache, v_cache, block_tables, step, KVH, p
                 s = softcap * torch.tanh(s / softcap)
             if slopes is not None:
                 s = s - float(slopes[h]) * (i - j).float()
-            p = torch.softmax(s.masked_fill(~ok, float("-inf")), -1)
+            s = s.masked_fill(~ok, float("-inf"))
+            if sinks is not None:
+                s = torch.cat([s, sinks[h].float().expand(Tq, 1)], -1)
+            p = torch.softmax(s, -1)[:, :seq_len]
             out[qs:qe, h] = (p @ vv[:, h // G]).to(out.dtype)
 
 
@@ -430,5 +475,5 @@ for _name, _fn in (("delta_prepare", _delta_prepare), ("delta_scan", _delta_scan
                    ("head_gated_rmsnorm", _head_gated_rmsnorm), ("rms_rows", _rms_rows),
                    ("qk_rownorm_write", _qk_rownorm_write), ("latent_kv_write", _latent_kv_write),
                    ("rotate_pairs", _rotate_pairs), ("batched_linear", _batched_linear),
-                   ("attention_biased", _attention_biased)):
+                   ("attention_biased", _attention_biased), ("rope_headnorm_write", _rope_headnorm_write)):
     setattr(TwinOps, _name, _fn)

@@ -1,14 +1,14 @@
 """Cache manager: paged keys/values with one block table per (request, group), and fixed-size
 per-request state slots.
 
-Runs of the schedule whose mixers want the same thing from the cache (same kv heads, head size
-and window) form a GROUP.  A group has its own pool ``[runs, 2, pages, kv_heads, page, head_dim]``
+Runs of the schedule whose mixers want the same thing from the cache (same kv heads, head sizes,
+window and block size) form a GROUP.  A group has its own pool ``[runs, 2, pages, kv_heads, page, head_dim]``
 (where a mixer's value rows are wider or narrower than its key rows: two tensors
 ``[runs, pages, kv_heads, page, head_dim]`` and ``[runs, pages, kv_heads, page, value_dim]``)
 (the reference's single ``[L, 2, NB, KVH, 16, D]`` tensor, turingserve/engine/builder.py:76-80,
 is the one-group case), its own allocator and, per request, its own block table.  Pages go back
-to the group's free list when a request is released, and, in a windowed group, as soon as the
-window has passed them; freed pages are re-issued first-in first-out.
+to the group's free list when a request is released, and, in a group with a window or with blocks
+of positions, as soon as no later position can see them; freed pages are re-issued first-in first-out.
 
 Slot arithmetic as turingserve/kv/kv_manager.py:17-40:
 slot(pos) = table[pos // page] * page + pos % page; pages needed = ceil(tokens / page) - held.
@@ -89,7 +89,7 @@ class CacheManager:
         for r, n in enumerate(needs):
             if n.cache is None or n.cache_from is not None:
                 continue
-            key = (n.cache.num_kv_heads, n.cache.head_dim, n.cache.window, n.cache.v_dim)
+            key = (n.cache.num_kv_heads, n.cache.head_dim, n.cache.window, n.cache.v_dim, n.cache.chunk)
             if key not in keys:
                 keys[key] = len(self.groups)
                 self.groups.append(CacheGroup(n.cache, [], num_pages))
@@ -199,11 +199,14 @@ class CacheManager:
         if self.groups and rc.num_tokens > len(rc.tables[0]) * self.page_size:
             raise RuntimeError("advance() beyond the pages that were grown")
         for gi, g in enumerate(self.groups):
-            w = g.need.window
-            if w is None:
+            w, c = g.need.window, g.need.chunk
+            if w is None and c is None:
                 continue
-            # the next query is at position >= num_tokens and sees keys >= num_tokens - w + 1
-            first_needed = max(0, rc.num_tokens - w + 1)
+            # the next query is at position >= num_tokens and sees keys >= num_tokens - w + 1, and with blocks
+            # of c positions no key before the block that position lies in
+            first_needed = max(0, rc.num_tokens - w + 1) if w is not None else 0
+            if c is not None:
+                first_needed = max(first_needed, rc.num_tokens // c * c)
             keep_from = first_needed // self.page_size
             table = rc.tables[gi]
             for p in range(rc.first_live_page[gi], min(keep_from, len(table))):

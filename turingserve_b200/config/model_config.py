@@ -59,11 +59,13 @@ class AttentionSpec:
 
 @dataclass(frozen=True)
 class GatedMLPSpec:
-    """Dense gated feed-forward: down(act(gate(x)) * up(x))."""
+    """Dense gated feed-forward: down(act(gate(x)) * up(x)).  ``names``: the local tensor names of the gate, up
+    and down weights."""
 
     intermediate_size: int
     activation: str = "silu"
     bias: bool = False
+    names: tuple[str, str, str] = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
     kind: str = "gated_mlp"
 
 
@@ -75,6 +77,59 @@ class StreamRMSNormSpec:
     eps: float
     weight_name: str = "weight"         # local tensor name of the scale ('' = the norm's prefix itself)
     kind: str = "rmsnorm_stream"
+
+
+@dataclass(frozen=True)
+class StreamLayerNormSpec:
+    """Layer norm of a residual stream that is kept in 32-bit whatever the engine's type:
+    (x - mean) / sqrt(mean((x - mean)^2) + eps) * weight + bias, all in 32-bit, rounded once."""
+
+    eps: float
+    weight_name: str = "weight"         # local tensor names ('' = the norm's prefix itself)
+    bias_name: str = "bias"
+    kind: str = "layernorm_stream"
+
+
+@dataclass(frozen=True)
+class BranchJoinSpec:
+    """How the outputs of a layer's branches enter the residual stream: x <- x + scale * (their sum)."""
+
+    scale: float = 1.0
+    kind: str = "branch_join"
+
+
+@dataclass(frozen=True)
+class HalfRotarySpec:
+    """Rotary position encoding over the first ``dims`` dimensions of a head, dimension i paired with dimension
+    i + dims/2: the pair (u, v) at position p becomes (u cos a - v sin a, v cos a + u sin a), a = p * f_i,
+    f_i = base^(-2i/dims).  The angle is a 32-bit product of the position and the frequency, so no table over
+    positions exists and no longest sequence has to be known."""
+
+    base: float
+    dims: int
+    kind: str = "rope_half"
+
+
+@dataclass(frozen=True)
+class SinkAttentionSpec:
+    """Grouped-query softmax attention over keys ``key_dim`` and values ``value_dim`` wide, no biases.
+    ``position``: a rotation of q and k (not v).  ``qk_norm_eps`` not None: after the rotation every head of q
+    and k is divided by its root mean square (eps inside the root, no learned weight).  ``chunk`` c: position i
+    sees j <= i only inside its own block of c positions, floor(i / c) = floor(j / c), blocks counted from the
+    sequence's position 0.  ``window`` w: only i - w < j.  ``sinks``: the softmax's denominator also holds
+    exp(sink_h), a learned number per head without key or value, unscaled, counted once."""
+
+    num_heads: int
+    num_kv_heads: int
+    key_dim: int
+    value_dim: int
+    scale: float
+    position: Any = None
+    qk_norm_eps: float | None = None
+    chunk: int | None = None
+    window: int | None = None
+    sinks: bool = True
+    kind: str = "sink_attention"
 
 
 @dataclass(frozen=True)
@@ -207,7 +262,10 @@ class RoutedMLPSpec:
     """Mixture of small feed-forwards down(act(up(.))) without biases: every token goes to the ``top_k``
     experts with the largest router scores.  ``scoring``: sigmoid | softmax of the router logits (32-bit);
     ``renormalize``: the chosen scores divided by their sum; ``weight_on``: "input" (the score multiplies
-    what the expert reads) or "output" (what it returns)."""
+    what the expert reads) or "output" (what it returns).  ``gated``: the experts are
+    down(act(gate(.)) * up(.)).  ``correction``: a learned vector added to the scores for the choice only (the
+    weights stay the scores).  ``identity``: so many more router outputs, behind the ``num_experts`` with
+    tensors, are experts that return their input."""
 
     num_experts: int
     top_k: int
@@ -216,6 +274,9 @@ class RoutedMLPSpec:
     scoring: str = "sigmoid"
     renormalize: bool = False
     weight_on: str = "input"
+    gated: bool = False
+    correction: bool = False
+    identity: int = 0
     kind: str = "routed_mlp"
 
 
@@ -273,6 +334,9 @@ class LayerRun:
     # the embedding rows of the step are added to the stream before this run (a model that runs a span of
     # layers several times re-injects its input at the start of every later pass)
     add_embedding: bool = False
+    # this run opens pass number ``opens_pass`` of a span of layers that runs several times: the model adds
+    # that pass's own vector to the stream before it (None: it opens none)
+    opens_pass: int | None = None
 
 
 @dataclass(frozen=True)

@@ -123,3 +123,5 @@ def _load_builtin() -> None:
         from turingserve_b200.models import komirax  # noqa: F401
     if "Pizunex" not in _ARCHITECTURES:
         from turingserve_b200.models import pizunex  # noqa: F401
+    if "Vofinex" not in _ARCHITECTURES:
+        from turingserve_b200.models import vofinex  # noqa: F401

@@ -1,8 +1,10 @@
 // Paged grouped-query attention with a score that is more than a scaled dot product, any sizes, 32-bit
 // arithmetic whatever the storage type:
 //     s = q.k * scale;   s <- cap * tanh(s / cap)  (cap > 0);   s <- s - slope_h * (i - j)  (slopes given)
-// for the query at position i and the key at position j <= i, and with a window w only j > i - w; ordinary
-// softmax over the visible keys; a request without context gives zeros.  Key rows (Dk wide) and value rows
+// for the query at position i and the key at position j <= i, with a window w only j > i - w, and with blocks of c
+// positions (counted from the sequence's position 0) only j >= floor(i / c) * c; softmax over the visible keys, whose
+// denominator also holds exp(sink_h) when sinks are given (a learned number per head that has no key and no value:
+// the weights of a row then sum to less than one); a request without context gives zeros.  Key rows (Dk wide) and value rows
 // (Dv wide) have widths of their own; with no value tensor the values ARE the first Dv columns of the key rows
 // (a cache that keeps one latent row a token serves all heads as keys and as values).  Queries and outputs
 // are addressed by a token stride and a head stride, so they may be column slices of wider rows.
@@ -23,6 +25,17 @@ constexpr int AB_WARPS = 4;
 constexpr int AB_RPW = AB_ROWS / AB_WARPS;
 constexpr int AB_MAX_DPL = 16;  // Dv <= 512
 
+// 1 / (l + exp(sink - m)) for sums l taken against the maximum m: what the unnormalised output is multiplied by.
+// Against the larger of m and the sink, so that neither exponential can overflow.  No visible key: 0.
+__device__ __forceinline__ float sink_inverse(float m, float l, const float* sink) {
+  if (!(l > 0.f)) return 0.f;
+  if (sink == nullptr) return 1.f / l;
+  const float s = *sink;
+  const float top = fmaxf(m, s);
+  const float down = expf(m - top);
+  return down / (l * down + expf(s - top));
+}
+
 template <typename T, int DPL>
 __global__ void __launch_bounds__(AB_WARPS * 32)
 attention_biased_kernel(T* __restrict__ out, int out_ts, int out_hs, const T* __restrict__ q, int q_ts, int q_hs,
@@ -30,7 +43,8 @@ attention_biased_kernel(T* __restrict__ out, int out_ts, int out_hs, const T* __
                         const int* __restrict__ block_tables, const int* __restrict__ q_start,
                         const int* __restrict__ seq_lens, int table_width, int H, int KVH, int Dk, int Dv, int page,
                         float scale, float softcap, const float* __restrict__ slopes, int window, int splits,
-                        float* __restrict__ scratch, int* __restrict__ counters) {
+                        float* __restrict__ scratch, int* __restrict__ counters, int chunk,
+                        const float* __restrict__ sinks) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float smem[];
@@ -71,6 +85,7 @@ attention_biased_kernel(T* __restrict__ out, int out_ts, int out_hs, const T* __
   const int t_lo = row0 / G, t_hi = last_row / G;
   int j_hi = prefix + t_hi;                                           // last key any row of the tile sees
   int j_lo = window > 0 ? max(0, prefix + t_lo - window + 1) : 0;
+  if (chunk > 0) j_lo = max(j_lo, (prefix + t_lo) / chunk * chunk);      // (a block's start never moves back with the position)
   if (my_splits > 1) {
     // this block's share of the key tiles
     const int n_tiles = (j_hi - j_lo) / AB_KT + 1;
@@ -92,6 +107,7 @@ attention_biased_kernel(T* __restrict__ out, int out_ts, int out_hs, const T* __
     const int t = row / G;
     p_row[r] = (row < n_rows) ? prefix + t : -1;
     lo_row[r] = (window > 0) ? max(0, p_row[r] - window + 1) : 0;
+    if (chunk > 0 && p_row[r] >= 0) lo_row[r] = max(lo_row[r], p_row[r] / chunk * chunk);
     slope[r] = (slopes != nullptr && row < n_rows) ? slopes[kvh * G + row % G] : 0.f;
   }
 
@@ -166,7 +182,7 @@ attention_biased_kernel(T* __restrict__ out, int out_ts, int out_hs, const T* __
       const int row = row0 + warp * AB_RPW + r;
       if (row >= n_rows) continue;
       const int t = row / G, g = row % G;
-      const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+      const float inv = sink_inverse(m[r], l[r], sinks != nullptr ? sinks + kvh * G + g : nullptr);
       T* o = out + (size_t)(qs + t) * out_ts + (size_t)(kvh * G + g) * out_hs;
 #pragma unroll
       for (int i = 0; i < DPL; ++i) {
@@ -228,7 +244,7 @@ attention_biased_kernel(T* __restrict__ out, int out_ts, int out_hs, const T* __
       }
     }
     const int t = row / G, g = row % G;
-    const float inv = ll > 0.f ? 1.f / ll : 0.f;
+    const float inv = sink_inverse(mm, ll, sinks != nullptr ? sinks + kvh * G + g : nullptr);
     T* dst = out + (size_t)(qs + t) * out_ts + (size_t)(kvh * G + g) * out_hs;
 #pragma unroll
     for (int i = 0; i < DPL; ++i) {
@@ -242,7 +258,7 @@ template <typename T, int DPL>
 int launch(void* out, int out_ts, int out_hs, const void* q, int q_ts, int q_hs, const void* k_cache, const void* v_cache,
            const int* block_tables, const int* q_start, const int* seq_lens, int B, int table_width, int max_q_len, int H,
            int KVH, int Dk, int Dv, int page, float scale, float softcap, const float* slopes, int window, int splits,
-           float* scratch, int* counters, cudaStream_t s) {
+           float* scratch, int* counters, int chunk, const float* sinks, cudaStream_t s) {
   const int G = H / KVH;
   const size_t smem = sizeof(float) * ((size_t)AB_ROWS * Dk + (size_t)AB_KT * (Dk + 1) + (v_cache ? (size_t)AB_KT * Dv : 0));
   static size_t configured = 0;
@@ -254,7 +270,7 @@ int launch(void* out, int out_ts, int out_hs, const void* q, int q_ts, int q_hs,
   dim3 grid(ceil_div(max_q_len * G, AB_ROWS) * splits, KVH, B);
   ts_launch(attention_biased_kernel<T, DPL>, dim3(grid), dim3(AB_WARPS * 32), smem, s, (T*)out, out_ts, out_hs, (const T*)q,
             q_ts, q_hs, (const T*)k_cache, (const T*)v_cache, block_tables, q_start, seq_lens, table_width, H, KVH, Dk, Dv,
-            page, scale, softcap, slopes, window, splits, scratch, counters);
+            page, scale, softcap, slopes, window, splits, scratch, counters, chunk, sinks);
   TS_LAUNCH_CHECK();
 }
 
@@ -268,13 +284,14 @@ TS_API long long ts_attention_biased_scratch_floats(int B, int KVH, int H, int m
 }
 
 // k_cache [pages, KVH, page, Dk]; v_cache [pages, KVH, page, Dv] or null (values = first Dv columns of the key
-// rows).  softcap <= 0: no cap; slopes null: no distance bias; window <= 0: none.  splits > 1 needs scratch
+// rows).  softcap <= 0: no cap; slopes null: no distance bias; window <= 0: none; chunk <= 0: no blocks; sinks
+// (32-bit [H]) null: none.  splits > 1 needs scratch
 // (ts_attention_biased_scratch_floats) and zeroed counters, one per (request, kv head, row tile).
 TS_API int ts_attention_biased(void* out, int out_ts, int out_hs, const void* q, int q_ts, int q_hs, const void* k_cache,
                                const void* v_cache, const int* block_tables, const int* q_start, const int* seq_lens, int B,
                                int table_width, int max_q_len, int H, int KVH, int Dk, int Dv, int page, float scale,
                                float softcap, const float* slopes, int window, int splits, float* scratch, int* counters,
-                               int dtype, void* stream) {
+                               int dtype, int chunk, const float* sinks, void* stream) {
   if (B <= 0 || max_q_len <= 0) return 0;
   if (KVH <= 0 || H % KVH) TS_REFUSE(TS_ERR_SHAPE, "ts_attention_biased: %d heads over %d kv heads", H, KVH);
   if (Dk <= 0 || Dv <= 0 || Dv > 32 * AB_MAX_DPL || (v_cache == nullptr && Dv > Dk))
@@ -287,7 +304,7 @@ TS_API int ts_attention_biased(void* out, int out_ts, int out_hs, const void* q,
   const int dpl = ceil_div(Dv, 32);
 #define TS_AB(TT, N)                                                                                                   \
   return launch<TT, N>(out, out_ts, out_hs, q, q_ts, q_hs, k_cache, v_cache, block_tables, q_start, seq_lens, B, table_width, \
-                       max_q_len, H, KVH, Dk, Dv, page, scale, softcap, slopes, window, splits, scratch, counters, s)
+                       max_q_len, H, KVH, Dk, Dv, page, scale, softcap, slopes, window, splits, scratch, counters, chunk, sinks, s)
 #define TS_AB_T(TT)                     \
   do {                                  \
     if (dpl <= 2) TS_AB(TT, 2);         \

@@ -1,5 +1,5 @@
-// The attention of attention_biased.cu (capped scores, distance bias per head, window, values of their own width or
-// inside the key rows) on the tensor cores, bfloat16 storage, for key rows that are a multiple of 64 wide.
+// The attention of attention_biased.cu (capped scores, distance bias per head, window, blocks of positions, a sink in
+// the softmax's denominator, values of their own width or inside the key rows) on the tensor cores, bfloat16 storage, for key rows that are a multiple of 64 wide.
 //
 // Work split as in the prompt-portion kernel: one block per (tile of 64 query ROWS, kv head, request), a row being
 // one (token, head-in-group) pair, four warps of 16 rows (m16n8k16), keys 64 at a time through a cp.async pipeline
@@ -43,7 +43,8 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
                             const int* __restrict__ block_tables, const int* __restrict__ q_start,
                             const int* __restrict__ seq_lens, int table_width, int H, int KVH, int page, float scale,
                             float softcap, const float* __restrict__ slopes, int window, int v_chunks, int splits,
-                            float* __restrict__ scratch, int* __restrict__ counters) {
+                            float* __restrict__ scratch, int* __restrict__ counters, int block_of,
+                            const float* __restrict__ sinks) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int CHK = DK / 8, KS = DK / 16, NT = DV / 8, CHV = DV / 8;
@@ -74,8 +75,8 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
   __shared__ int last_flag;
 
   // this thread's two rows
-  int pos[2];
-  float slope[2];
+  int pos[2], lo[2];                                                 // the row's position and the first key it sees
+  float slope[2], sink2[2];                                          // (the sink in the exp2 domain; -inf: none)
   bf16* optr[2];
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
@@ -83,11 +84,16 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
     if (row < n_rows) {
       const int t = row / G, g = row % G;
       pos[r] = prefix + t;
+      lo[r] = window > 0 ? max(0, pos[r] - window + 1) : 0;
+      if (block_of > 0) lo[r] = max(lo[r], pos[r] / block_of * block_of);
       slope[r] = slopes != nullptr ? slopes[kvh * G + g] : 0.f;
+      sink2[r] = sinks != nullptr ? sinks[kvh * G + g] * BM_LOG2E : -INFINITY;
       optr[r] = out + (size_t)(qs + t) * out_ts + (size_t)(kvh * G + g) * out_hs + chunk * DV;
     } else {
       pos[r] = -1;                                                   // sees nothing, writes nothing
+      lo[r] = 0;
       slope[r] = 0.f;
+      sink2[r] = -INFINITY;
       optr[r] = nullptr;
     }
   }
@@ -105,6 +111,7 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
   const int last_row = min(row0 + BM_ROWS, n_rows) - 1;
   int j_hi = prefix + last_row / G;
   int j_lo = window > 0 ? max(0, prefix + row0 / G - window + 1) : 0;
+  if (block_of > 0) j_lo = max(j_lo, (prefix + row0 / G) / block_of * block_of);
   if (my_splits > 1) {
     const int all = (j_hi - j_lo) / BM_TILE + 1;
     const int per = (all + my_splits - 1) / my_splits;
@@ -177,7 +184,8 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
     const unsigned char* vs_ = V_IN_K ? ks_ : v_s + (size_t)(t % STAGES) * BM_TILE * DV * 2;
     const int j0 = j_lo + t * BM_TILE;
     const bool in_future = j0 > w_pos_hi;                                          // warp-uniform
-    const bool in_past = window > 0 && (j0 + BM_TILE - 1) < (w_pos_lo - window + 1);
+    const bool in_past = (window > 0 && (j0 + BM_TILE - 1) < (w_pos_lo - window + 1)) ||
+                         (block_of > 0 && w_pos_lo >= 0 && (j0 + BM_TILE - 1) < w_pos_lo / block_of * block_of);
     if (!in_future && !in_past) {
       float s_acc[NTW][4];
 #pragma unroll
@@ -208,7 +216,7 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
           float v = s_acc[nt][e] * scale;
           if (softcap > 0.f) v = capped(v, softcap, inv_cap);
           v = (v - slope[e >> 1] * (float)(p - j)) * BM_LOG2E;
-          const bool ok = (j <= p) && (window <= 0 || j > p - window) && (j <= j_hi);
+          const bool ok = (j <= p) && (j >= lo[e >> 1]) && (j <= j_hi);
           v = ok ? v : -INFINITY;
           s_acc[nt][e] = v;
           mx[e >> 1] = fmaxf(mx[e >> 1], v);
@@ -279,7 +287,13 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       if (optr[r] == nullptr) continue;
-      const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
+      float inv = 0.f;
+      if (l_run[r] > 0.f) {
+        // the sink joins the denominator; both against the larger of the running maximum and the sink
+        const float top = fmaxf(m_run[r], sink2[r]);
+        const float down = exp2f(m_run[r] - top);
+        inv = down / (l_run[r] * down + exp2f(sink2[r] - top));
+      }
 #pragma unroll
       for (int i = 0; i < NT; ++i) {
         const int d = i * 8 + (lane & 3) * 2;
@@ -348,7 +362,13 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
       m_m[row * BM_MAX_RECORDS + k] = w;
       ll = fmaf(l_m[row * BM_MAX_RECORDS + k], w, ll);
     }
-    const float inv = ll > 0.f ? 1.f / ll : 0.f;
+    float inv = 0.f;
+    if (ll > 0.f) {
+      const float sk = sinks != nullptr ? sinks[kvh * G + row] * BM_LOG2E : -INFINITY;
+      const float top = fmaxf(mm, sk);
+      const float down = exp2f(mm - top);
+      inv = down / (ll * down + exp2f(sk - top));
+    }
     for (int k = 0; k < n_rec; ++k) m_m[row * BM_MAX_RECORDS + k] *= inv;
   }
   __syncthreads();
@@ -379,7 +399,7 @@ template <int DK, int DV, bool V_IN_K, int STAGES, int SPREAD>
 int launch(bf16* out, int out_ts, int out_hs, const bf16* q, int q_ts, int q_hs, const bf16* k_cache, const bf16* v_cache,
            const int* block_tables, const int* q_start, const int* seq_lens, int B, int table_width, int max_q_len, int H,
            int KVH, int page, float scale, float softcap, const float* slopes, int window, int v_chunks, int splits,
-           float* scratch, int* counters, cudaStream_t s) {
+           float* scratch, int* counters, int block_of, const float* sinks, cudaStream_t s) {
   const size_t smem = (size_t)BM_ROWS * DK * 2 + (size_t)STAGES * BM_TILE * DK * 2 + (V_IN_K ? 0 : (size_t)STAGES * BM_TILE * DV * 2);
   static bool configured = false;
   if (!configured) {
@@ -392,7 +412,7 @@ int launch(bf16* out, int out_ts, int out_hs, const bf16* q, int q_ts, int q_hs,
   dim3 grid(ceil_div(max_q_len * G, BM_ROWS) * v_chunks * splits, KVH, B);
   ts_launch(attention_biased_mma_kernel<DK, DV, V_IN_K, STAGES, SPREAD>, dim3(grid), dim3(BM_WARPS * 32), smem, s, out, out_ts, out_hs, q,
             q_ts, q_hs, k_cache, v_cache, block_tables, q_start, seq_lens, table_width, H, KVH, page, scale, softcap, slopes,
-            window, v_chunks, splits, scratch, counters);
+            window, v_chunks, splits, scratch, counters, block_of, sinks);
   TS_LAUNCH_CHECK();
 }
 
@@ -431,7 +451,7 @@ TS_API int ts_attention_biased_mma(void* out, int out_ts, int out_hs, const void
                                    const void* v_cache, const int* block_tables, const int* q_start, const int* seq_lens,
                                    int B, int table_width, int max_q_len, int H, int KVH, int Dk, int Dv, int page,
                                    float scale, float softcap, const float* slopes, int window, int splits, float* scratch,
-                                   int* counters, int spread, void* stream) {
+                                   int* counters, int spread, int block_of, const float* sinks, void* stream) {
   if (B <= 0 || max_q_len <= 0) return 0;
   const int v_in_k = v_cache == nullptr;
   const int inst = (KVH > 0 && H % KVH == 0) ? instance_of(Dk, Dv, v_in_k) : 0;
@@ -451,14 +471,14 @@ TS_API int ts_attention_biased_mma(void* out, int out_ts, int out_hs, const void
     if (spread && groups == 1)                                                                                                \
       return launch<DKK, DVV, VK, ST, 1>((bf16*)out, out_ts, out_hs, (const bf16*)q, q_ts, q_hs, (const bf16*)k_cache,        \
                                          (const bf16*)v_cache, block_tables, q_start, seq_lens, B, table_width, max_q_len,    \
-                                         H, KVH, page, scale, softcap, slopes, window, CHUNKS, splits, scratch, counters, s); \
+                                         H, KVH, page, scale, softcap, slopes, window, CHUNKS, splits, scratch, counters, block_of, sinks, s); \
     if (spread)                                                                                                               \
       return launch<DKK, DVV, VK, ST, 2>((bf16*)out, out_ts, out_hs, (const bf16*)q, q_ts, q_hs, (const bf16*)k_cache,        \
                                          (const bf16*)v_cache, block_tables, q_start, seq_lens, B, table_width, max_q_len,    \
-                                         H, KVH, page, scale, softcap, slopes, window, CHUNKS, splits, scratch, counters, s); \
+                                         H, KVH, page, scale, softcap, slopes, window, CHUNKS, splits, scratch, counters, block_of, sinks, s); \
     return launch<DKK, DVV, VK, ST, 0>((bf16*)out, out_ts, out_hs, (const bf16*)q, q_ts, q_hs, (const bf16*)k_cache,      \
                                            (const bf16*)v_cache, block_tables, q_start, seq_lens, B, table_width, max_q_len,  \
-                                           H, KVH, page, scale, softcap, slopes, window, CHUNKS, splits, scratch, counters, s); \
+                                           H, KVH, page, scale, softcap, slopes, window, CHUNKS, splits, scratch, counters, block_of, sinks, s); \
   } while (0)
   if (inst == 1) TS_BM(64, 64, false, 3, 1);
   if (inst == 2) TS_BM(128, 128, false, 2, 1);                        // (two stages: 80 KB a block, so two blocks share an SM)

@@ -4,17 +4,20 @@
 // chain can sit in a captured graph.
 //
 //   ts_router_topk     z = Wr x in 32-bit (one block a token, fixed summation order), score = sigmoid(z) or
-//                      softmax(z); the `top` largest by z (ties: the lower index); weights = their scores,
-//                      optionally divided by their sum.
+//                      softmax(z); the `top` largest by z (ties: the lower index), or, with a correction vector, by
+//                      score + correction; weights = their scores (never the correction), optionally divided by
+//                      their sum.
 //   ts_moe_align       pairs p = t * top + r sorted by expert: offsets[E + 1], order[P] (sorted place -> pair),
 //                      place[P] (pair -> sorted place), and the list of row tiles (expert, first row) the
-//                      grouped products walk.
+//                      grouped products walk; experts from `with_tiles` on get a group but no tiles (experts
+//                      without weights, whose output is their input).
 //   ts_grouped_linear  out[i, :] = act(a_i . W[e(i)]^T) for the sorted places i; a_i is row i of `x`, or, when
 //                      `order` is given, row order[i] / top of `x` times row_scale[order[i]] (rounded to the
 //                      storage type: the weighted input of an expert).  32-bit accumulation in ascending k
 //                      (FFMA; tensor cores for bfloat16 with K a multiple of 8): a row's result does not
 //                      depend on its tile-mates.
-//   ts_moe_combine     out[t, :] = sum over r (ascending) of (w[t, r] *) y[place[t * top + r], :], in 32-bit.
+//   ts_moe_combine     out[t, :] = sum over r (ascending) of (w[t, r] *) y[place[t * top + r], :], in 32-bit; a pair
+//                      whose sorted place is *pass_from or later contributes the token's own input row instead.
 #include "activations.cuh"
 #include "common.cuh"
 #include "mma_utils.cuh"
@@ -33,12 +36,14 @@ constexpr int RT_THREADS = 256;
 template <typename T>
 __global__ void __launch_bounds__(RT_THREADS)
 router_topk_kernel(int* __restrict__ idx_out, float* __restrict__ w_out, const T* __restrict__ x,
-                   const float* __restrict__ wr, int T_, int E, int K, int top, int softmax, int renorm) {
+                   const float* __restrict__ wr, int T_, int E, int K, int top, int softmax, int renorm,
+                   const float* __restrict__ correction) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float smem[];
   float* z = smem;                       // [E]
   float* part = smem + E;                // [RT_THREADS / 32][8]
+  float* pick = part + RT_THREADS / 32 * 8;   // [E] what the choice goes by, when it is not z itself
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   const T* xr = x + (size_t)t * K;
@@ -74,12 +79,19 @@ router_topk_kernel(int* __restrict__ idx_out, float* __restrict__ w_out, const T
     for (int e = lane; e < E; e += 32) d += expf(z[e] - zmax);
     denom = warp_sum(d);
   }
+  const float* by = z;
+  if (correction != nullptr) {
+    for (int e = lane; e < E; e += 32)
+      pick[e] = (softmax ? expf(z[e] - zmax) / denom : 1.f / (1.f + expf(-z[e]))) + correction[e];
+    by = pick;
+    __syncwarp();
+  }
   float total = 0.f;
   for (int r = 0; r < top; ++r) {
     float best = -INFINITY;
     int arg = 0x7fffffff;
     for (int e = lane; e < E; e += 32) {
-      const float v = z[e];
+      const float v = by[e];
       if (v > best) {              // ascending e: the first of equal values stays
         best = v;
         arg = e;
@@ -95,12 +107,14 @@ router_topk_kernel(int* __restrict__ idx_out, float* __restrict__ w_out, const T
       }
     }
     if (arg == 0x7fffffff) arg = 0;              // only when every score left is -inf or NaN
-    const float score = softmax ? expf(best - zmax) / denom : 1.f / (1.f + expf(-best));
+    const float logit = correction != nullptr ? z[arg] : best;
+    const float score = softmax ? expf(logit - zmax) / denom : 1.f / (1.f + expf(-logit));
     total += score;
     if (lane == 0) {
       idx_out[(size_t)t * top + r] = arg;
       w_out[(size_t)t * top + r] = score;
-      z[arg] = -INFINITY;
+      if (correction != nullptr) pick[arg] = -INFINITY;
+      else z[arg] = -INFINITY;
     }
     __syncwarp();
   }
@@ -112,7 +126,7 @@ router_topk_kernel(int* __restrict__ idx_out, float* __restrict__ w_out, const T
 // One block.  tiles: [0] = number of row tiles, then (expert, first sorted row) pairs.
 __global__ void __launch_bounds__(1024)
 moe_align_kernel(const int* __restrict__ idx, int P, int E, int* __restrict__ offsets, int* __restrict__ order,
-                 int* __restrict__ place, int* __restrict__ tiles, int tile_rows) {
+                 int* __restrict__ place, int* __restrict__ tiles, int tile_rows, int with_tiles) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ int sm_i[];
@@ -127,7 +141,7 @@ moe_align_kernel(const int* __restrict__ idx, int P, int E, int* __restrict__ of
     for (int e = 0; e < E; ++e) {
       offsets[e] = at;
       cursor[e] = at;
-      for (int r = 0; r < count[e]; r += tile_rows) {
+      for (int r = 0; e < with_tiles && r < count[e]; r += tile_rows) {
         tiles[1 + 2 * n] = e;
         tiles[2 + 2 * n] = at + r;
         ++n;
@@ -433,15 +447,18 @@ __global__ void moe_gather_kernel(T* __restrict__ xs, const T* __restrict__ x, c
 
 template <typename T>
 __global__ void moe_combine_kernel(T* __restrict__ out, const float* __restrict__ y, const int* __restrict__ place,
-                                   const float* __restrict__ pair_w, int top, int N) {
+                                   const float* __restrict__ pair_w, int top, int N, const T* __restrict__ x,
+                                   const int* __restrict__ pass_from) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
+  const int first_pass = pass_from != nullptr ? *pass_from : 0x7fffffff;
   for (int n = threadIdx.x; n < N; n += blockDim.x) {
     float acc = 0.f;
     for (int r = 0; r < top; ++r) {
       const size_t p = (size_t)t * top + r;
-      const float v = y[(size_t)place[p] * N + n];
+      const int at = place[p];
+      const float v = at >= first_pass ? to_f(x[(size_t)t * N + n]) : y[(size_t)at * N + n];
       acc += pair_w != nullptr ? pair_w[p] * v : v;
     }
     out[(size_t)t * N + n] = from_f<T>(acc);
@@ -453,30 +470,33 @@ __global__ void moe_combine_kernel(T* __restrict__ out, const float* __restrict_
 TS_API int ts_moe_tile_rows() { return GL_BM; }
 
 // x: [T, K] in `dtype`; wr: [E, K] 32-bit.  idx_out / w_out: [T, top].
+// correction: 32-bit [E] or null.
 TS_API int ts_router_topk(int* idx_out, float* w_out, const void* x, const float* wr, int T, int E, int K, int top,
-                          int softmax, int renorm, int dtype, void* stream) {
+                          int softmax, int renorm, int dtype, const float* correction, void* stream) {
   if (T <= 0) return 0;
   if (E <= 0 || top <= 0 || top > E) TS_REFUSE(TS_ERR_SHAPE, "ts_router_topk: top %d of %d experts", top, E);
   if (E > 2048) TS_REFUSE(TS_ERR_LIMIT, "ts_router_topk: %d experts (limit 2048)", E);
   cudaStream_t s = (cudaStream_t)stream;
-  const size_t smem = sizeof(float) * (E + RT_THREADS / 32 * 8);
+  const size_t smem = sizeof(float) * (2 * E + RT_THREADS / 32 * 8);
   if (dtype == TS_F32)
     ts_launch(router_topk_kernel<float>, dim3(T), dim3(RT_THREADS), smem, s, idx_out, w_out, (const float*)x, wr, T,
-              E, K, top, softmax, renorm);
+              E, K, top, softmax, renorm, correction);
   else if (dtype == TS_BF16)
     ts_launch(router_topk_kernel<bf16>, dim3(T), dim3(RT_THREADS), smem, s, idx_out, w_out, (const bf16*)x, wr, T,
-              E, K, top, softmax, renorm);
+              E, K, top, softmax, renorm, correction);
   else
     TS_REFUSE(TS_ERR_DTYPE, "ts_router_topk: dtype %d", dtype);
   TS_LAUNCH_CHECK();
 }
 
 // tiles needs 1 + 2 * (ceil(P / tile_rows) + E) ints.
-TS_API int ts_moe_align(const int* idx, int P, int E, int* offsets, int* order, int* place, int* tiles, void* stream) {
+// with_tiles: the experts [0, with_tiles) get row tiles (E: all of them).
+TS_API int ts_moe_align(const int* idx, int P, int E, int* offsets, int* order, int* place, int* tiles, int with_tiles,
+                        void* stream) {
   if (P <= 0) return 0;
   if (E > 4096) TS_REFUSE(TS_ERR_LIMIT, "ts_moe_align: %d experts (limit 4096)", E);
   ts_launch(moe_align_kernel, dim3(1), dim3(1024), sizeof(int) * 2 * E, (cudaStream_t)stream, idx, P, E, offsets, order,
-            place, tiles, GL_BM);
+            place, tiles, GL_BM, with_tiles);
   TS_LAUNCH_CHECK();
 }
 
@@ -545,14 +565,16 @@ TS_API int ts_grouped_linear(void* out, const void* x, const void* w, const int*
   TS_LAUNCH_CHECK();
 }
 
+// x (out's type, [T, N]) and pass_from (one int on the device): pairs sorted to place *pass_from or later add the
+// token's own row of x instead of a row of y; both null: none do.
 TS_API int ts_moe_combine(void* out, const float* y, const int* place, const float* pair_w, int T, int top, int N, int dtype,
-                          void* stream) {
+                          const void* x, const int* pass_from, void* stream) {
   if (T <= 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == TS_F32)
-    ts_launch(moe_combine_kernel<float>, dim3(T), dim3(256), 0, s, (float*)out, y, place, pair_w, top, N);
+    ts_launch(moe_combine_kernel<float>, dim3(T), dim3(256), 0, s, (float*)out, y, place, pair_w, top, N, (const float*)x, pass_from);
   else if (dtype == TS_BF16)
-    ts_launch(moe_combine_kernel<bf16>, dim3(T), dim3(256), 0, s, (bf16*)out, y, place, pair_w, top, N);
+    ts_launch(moe_combine_kernel<bf16>, dim3(T), dim3(256), 0, s, (bf16*)out, y, place, pair_w, top, N, (const bf16*)x, pass_from);
   else
     TS_REFUSE(TS_ERR_DTYPE, "ts_moe_combine: dtype %d", dtype);
   TS_LAUNCH_CHECK();

@@ -6,6 +6,9 @@
 //   ts_latent_kv_write   one cached row a token: [rms(latent) * w | rotated key part]
 //   ts_rotate_pairs      rotation of neighbouring pairs (2i, 2i+1), angle = position * freq[i] in 32-bit, cosine and
 //                        sine times a magnitude; strided source and destination
+//   ts_rope_headnorm_write  rotation of the pairs (i, i + R/2) of every q and k head, angle = position * freq[i] in 32-bit,
+//                        then each head over its root mean square (no weight); q in place, k and v rows into a cache
+//                        whose key and value rows have widths of their own
 //   ts_batched_linear    out[t, h, :] = w[h] x[t, h, :], a product per head over strided rows (FFMA, fixed k order; up to
 //                        16 rows: a warp an output column, streaming its weight row)
 #include "common.cuh"
@@ -235,6 +238,68 @@ batched_linear_rows_kernel(T* __restrict__ out, int out_ts, int out_hs, const T*
   }
 }
 
+// One warp a (token, head), RHN_WARPS heads a block.  The head's D values pass through shared memory: rotated in
+// 32-bit (dimension i < R/2 with dimension i + R/2, the rest as they are), then, with norm != 0, divided by
+// sqrt(mean of their squares + eps), rounded once; q heads go back where they came from, k heads into the key
+// cache.  The block with blockIdx.y == 0 also copies the token's value rows.  A slot of -1 caches nothing.
+constexpr int RHN_WARPS = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(RHN_WARPS * 32)
+rope_headnorm_write_kernel(T* __restrict__ proj, int stride, int k_off, int v_off, const int* __restrict__ positions,
+                           const float* __restrict__ freq, int rot_dims, int norm, float eps, T* __restrict__ k_cache,
+                           T* __restrict__ v_cache, const int* __restrict__ slots, int H, int G, int D, int V, int page) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float rhn_s[];
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int head = blockIdx.y * RHN_WARPS + warp;
+  const int slot = slots != nullptr ? slots[t] : -1;
+  T* row = proj + (size_t)t * stride;
+  if (head < H + G) {
+    float* x = rhn_s + warp * D;
+    T* src = head < H ? row + (size_t)head * D : row + k_off + (size_t)(head - H) * D;
+    const float pos = (float)positions[t];
+    const int half = rot_dims / 2;
+    float ss = 0.f;
+    for (int i = lane; i < half; i += 32) {
+      float sn, cs;
+      sincosf(pos * freq[i], &sn, &cs);
+      const float u = to_f(src[i]), v = to_f(src[i + half]);
+      const float a = u * cs - v * sn, b = v * cs + u * sn;
+      x[i] = a;
+      x[i + half] = b;
+      ss += a * a + b * b;
+    }
+    for (int i = rot_dims + lane; i < D; i += 32) {
+      const float v = to_f(src[i]);
+      x[i] = v;
+      ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    __syncwarp();
+    const float r = norm ? 1.f / sqrtf(ss / (float)D + eps) : 1.f;
+    T* dst = src;
+    if (head >= H) {
+      dst = nullptr;
+      if (slot >= 0) {
+        const size_t pg = slot / page, off = slot % page;
+        dst = k_cache + ((pg * G + (head - H)) * page + off) * D;
+      }
+    }
+    if (dst != nullptr)
+      for (int i = lane; i < D; i += 32) dst[i] = from_f<T>(x[i] * r);
+  }
+  if (blockIdx.y == 0 && slot >= 0 && v_cache != nullptr) {
+    const size_t pg = slot / page, off = slot % page;
+    for (int i = threadIdx.x; i < G * V; i += blockDim.x) {
+      const int g = i / V, d = i % V;
+      v_cache[((pg * G + g) * page + off) * V + d] = row[v_off + i];
+    }
+  }
+}
+
 int threads_for_row(int n) { return n >= 2048 ? 512 : (n >= 512 ? 256 : 128); }
 
 }  // namespace
@@ -291,6 +356,30 @@ TS_API int ts_rotate_pairs(void* dst, int dst_ts, int dst_hs, const void* src, i
   TS_BY_TYPE("ts_rotate_pairs",
              ts_launch(rotate_pairs_kernel<TT>, dim3(T), dim3(threads_for_row(H * R / 2)), 0, s, (TT*)dst, dst_ts, dst_hs,
                        (const TT*)src, src_ts, src_hs, positions, freq, magnitude, rot_dims, H, R));
+  TS_LAUNCH_CHECK();
+}
+
+// proj [T, stride]: q heads in columns [0, H D), k heads in [k_off, k_off + G D), value rows in [v_off, v_off + G V).
+// freq: 32-bit [rot_dims / 2].  k_cache [pages, G, page, D], v_cache [pages, G, page, V]; slots null: nothing is cached.
+TS_API int ts_rope_headnorm_write(void* proj, int stride, int k_off, int v_off, const int* positions, const float* freq,
+                                  int rot_dims, int norm, float eps, void* k_cache, void* v_cache, const int* slots, int T,
+                                  int H, int G, int D, int V, int page, int dtype, void* stream) {
+  if (T <= 0) return 0;
+  if (rot_dims < 0 || rot_dims % 2 || rot_dims > D) TS_REFUSE(TS_ERR_SHAPE, "ts_rope_headnorm_write: %d rotated dimensions of %d", rot_dims, D);
+  if (rot_dims > 0 && freq == nullptr) TS_REFUSE(TS_ERR_SHAPE, "ts_rope_headnorm_write: a rotation without frequencies");
+  if (D <= 0 || D > 4096) TS_REFUSE(TS_ERR_LIMIT, "ts_rope_headnorm_write: heads of %d (limit 4096)", D);
+  const int groups = ceil_div(H + G, RHN_WARPS);
+  if (groups > 65535) TS_REFUSE(TS_ERR_LIMIT, "ts_rope_headnorm_write: %d heads", H + G);
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t smem = sizeof(float) * RHN_WARPS * D;
+  if (smem > 48 * 1024) {
+    cudaError_t e1 = cudaFuncSetAttribute(rope_headnorm_write_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e2 = cudaFuncSetAttribute(rope_headnorm_write_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e1 != cudaSuccess || e2 != cudaSuccess) TS_REFUSE((int)(e1 != cudaSuccess ? e1 : e2), "ts_rope_headnorm_write: shared memory %zu", smem);
+  }
+  TS_BY_TYPE("ts_rope_headnorm_write",
+             ts_launch(rope_headnorm_write_kernel<TT>, dim3(T, groups), dim3(RHN_WARPS * 32), smem, s, (TT*)proj, stride, k_off,
+                       v_off, positions, freq, rot_dims, norm, eps, (TT*)k_cache, (TT*)v_cache, slots, H, G, D, V, page));
   TS_LAUNCH_CHECK();
 }
 

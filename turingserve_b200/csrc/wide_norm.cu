@@ -1,5 +1,6 @@
 // Row-wise kernels of models whose residual stream is kept in 32-bit whatever the engine's type:
-//   * the stream's own RMS norm, which first takes the pending branch outputs into the stream,
+//   * the stream's own norm (RMS, or a layer norm with mean, weight and bias), which first takes the pending
+//     branch outputs (times a constant) and a vector common to all rows into the stream,
 //   * an RMS norm over a 32-bit row with a sigmoid gate from a second tensor (the output stage of a
 //     linear-attention mixer),
 //   * one-input activations (tanh-form GELU, squared ReLU, SiLU).
@@ -9,26 +10,42 @@
 
 namespace {
 
-// stream[row] (+)= add1[row] + add2[row];  out[row] = T(stream * rsqrt(mean(stream^2) + eps) * w)
-// first != 0: the stream row is not read (this call starts it).  add1 / add2 may be null.
+// stream[row] (+)= alpha * add1[row] + alpha * add2[row] + vec;  out[row] = T(stream * rsqrt(mean(stream^2) + eps) * w),
+// or with a norm bias nb the layer norm T((stream - mean) * rsqrt(mean((stream - mean)^2) + eps) * w + nb).
+// first != 0: the stream row is not read (this call starts it).  add1 / add2 / vec (32-bit, one row) may be null.
 template <typename T, typename WT>
 __global__ void rmsnorm_wide_kernel(T* __restrict__ out, float* __restrict__ stream, const T* __restrict__ add1,
                                     const T* __restrict__ add2, const WT* __restrict__ w, float eps, int hidden,
-                                    int first) {
+                                    int first, float alpha, const float* __restrict__ vec, const WT* __restrict__ nb) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float scratch[32];
   const size_t base = (size_t)blockIdx.x * hidden;
-  float ss = 0.f;
+  float ss = 0.f, s1 = 0.f;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     float v = first ? 0.f : stream[base + i];
-    if (add1 != nullptr) v += to_f(add1[base + i]);
-    if (add2 != nullptr) v += to_f(add2[base + i]);
+    if (add1 != nullptr) v += alpha * to_f(add1[base + i]);
+    if (add2 != nullptr) v += alpha * to_f(add2[base + i]);
+    if (vec != nullptr) v += vec[i];
     stream[base + i] = v;
     ss += v * v;
+    s1 += v;
+  }
+  if (out == nullptr) return;
+  if (nb != nullptr) {
+    const float mean = block_sum(s1, scratch) / (float)hidden;
+    float dev = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      const float d = stream[base + i] - mean;
+      dev += d * d;
+    }
+    dev = block_sum(dev, scratch);
+    const float rstd = 1.f / sqrtf(dev / (float)hidden + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+      out[base + i] = from_f<T>((stream[base + i] - mean) * rstd * to_f(w[i]) + to_f(nb[i]));
+    return;
   }
   ss = block_sum(ss, scratch);
-  if (out == nullptr) return;
   const float rstd = 1.f / sqrtf(ss / (float)hidden + eps);
   for (int i = threadIdx.x; i < hidden; i += blockDim.x)
     out[base + i] = from_f<T>(stream[base + i] * rstd * to_f(w[i]));
@@ -40,13 +57,14 @@ template <typename T, typename WT, int CH>
 __global__ void __launch_bounds__(256)
 rmsnorm_wide_vec_kernel(T* __restrict__ out, float* __restrict__ stream, const T* __restrict__ add1,
                         const T* __restrict__ add2, const WT* __restrict__ w, float eps, int hidden, int first,
-                        const float* __restrict__ part, int splits, size_t split_stride, const T* __restrict__ bias) {
+                        const float* __restrict__ part, int splits, size_t split_stride, const T* __restrict__ bias,
+                        float alpha, const float* __restrict__ vec, const WT* __restrict__ nb) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float scratch[32];
   const size_t base = (size_t)blockIdx.x * hidden;
   float v[CH][4];
-  float ss = 0.f;
+  float ss = 0.f, s1 = 0.f;
 #pragma unroll
   for (int c = 0; c < CH; ++c) {
     const int i = (c * blockDim.x + threadIdx.x) * 4;
@@ -63,19 +81,49 @@ rmsnorm_wide_vec_kernel(T* __restrict__ out, float* __restrict__ stream, const T
         }
         const float pv[4] = {p4.x, p4.y, p4.z, p4.w};
 #pragma unroll
-        for (int k = 0; k < 4; ++k) v[c][k] += round_to<T>(pv[k] + (bias != nullptr ? to_f(bias[i + k]) : 0.f));
+        for (int k = 0; k < 4; ++k) v[c][k] += alpha * round_to<T>(pv[k] + (bias != nullptr ? to_f(bias[i + k]) : 0.f));
       }
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        if (add1 != nullptr) v[c][k] += to_f(add1[base + i + k]);
-        if (add2 != nullptr) v[c][k] += to_f(add2[base + i + k]);
+        if (add1 != nullptr) v[c][k] += alpha * to_f(add1[base + i + k]);
+        if (add2 != nullptr) v[c][k] += alpha * to_f(add2[base + i + k]);
+        if (vec != nullptr) v[c][k] += vec[i + k];
         ss += v[c][k] * v[c][k];
+        s1 += v[c][k];
       }
       *reinterpret_cast<float4*>(stream + base + i) = make_float4(v[c][0], v[c][1], v[c][2], v[c][3]);
     }
   }
-  ss = block_sum(ss, scratch);
   if (out == nullptr) return;
+  if (nb != nullptr) {
+    // layer norm: the deviations from the mean are taken from the registers, so the variance is a sum of squares of
+    // small numbers and not a difference of large ones
+    const float mean = block_sum(s1, scratch) / (float)hidden;
+    float dev = 0.f;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int i = (c * blockDim.x + threadIdx.x) * 4;
+      if (i < hidden) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          v[c][k] -= mean;
+          dev += v[c][k] * v[c][k];
+        }
+      }
+    }
+    dev = block_sum(dev, scratch);
+    const float rstd = 1.f / sqrtf(dev / (float)hidden + eps);
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int i = (c * blockDim.x + threadIdx.x) * 4;
+      if (i < hidden) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) out[base + i + k] = from_f<T>(v[c][k] * rstd * to_f(w[i + k]) + to_f(nb[i + k]));
+      }
+    }
+    return;
+  }
+  ss = block_sum(ss, scratch);
   const float rstd = 1.f / sqrtf(ss / (float)hidden + eps);
 #pragma unroll
   for (int c = 0; c < CH; ++c) {
@@ -137,9 +185,13 @@ int threads_for(int n) { return n >= 2048 ? 512 : (n >= 512 ? 256 : 128); }
 // product's epilogue would have done.
 TS_API int ts_rmsnorm_wide_takes_parts(int hidden) { return hidden % 4 == 0 && hidden <= 4 * 4 * 256; }
 
+//
+// alpha multiplies what is added (add1, add2, the product); vec (32-bit [hidden], may be null) is added to every row;
+// nbias (the type of w, may be null): with it the norm is a layer norm (mean taken off, variance about the mean,
+// times w plus nbias) instead of the RMS norm.
 TS_API int ts_rmsnorm_wide(void* out, float* stream, const void* add1, const void* add2, const void* w, float eps,
                            int T, int hidden, int first, int dtype, int w_dtype, const float* part, int splits,
-                           const void* bias, void* stream_) {
+                           const void* bias, float alpha, const float* vec, const void* nbias, void* stream_) {
   if (T <= 0) return 0;
   if (first && add1 == nullptr && part == nullptr) TS_REFUSE(TS_ERR_SHAPE, "ts_rmsnorm_wide: a stream starts from a tensor");
   if (part != nullptr && (!ts_rmsnorm_wide_takes_parts(hidden) || ((uintptr_t)stream & 15) || ((uintptr_t)part & 15)))
@@ -151,7 +203,7 @@ TS_API int ts_rmsnorm_wide(void* out, float* stream, const void* add1, const voi
     const int tv = ((hidden / 4 + ch - 1) / ch + 31) / 32 * 32;
 #define TS_WV(TT, WT, CH)                                                                                           \
   ts_launch(rmsnorm_wide_vec_kernel<TT, WT, CH>, dim3(T), dim3(tv), 0, s, (TT*)out, stream, (const TT*)add1, (const TT*)add2, \
-            (const WT*)w, eps, hidden, first, part, splits, (size_t)T * hidden, (const TT*)bias)
+            (const WT*)w, eps, hidden, first, part, splits, (size_t)T * hidden, (const TT*)bias, alpha, vec, (const WT*)nbias)
 #define TS_WVC(TT, WT)      \
   do {                      \
     if (ch == 1) TS_WV(TT, WT, 1); \
@@ -168,7 +220,7 @@ TS_API int ts_rmsnorm_wide(void* out, float* stream, const void* add1, const voi
   }
 #define TS_WN(TT, WT)                                                                                         \
   ts_launch(rmsnorm_wide_kernel<TT, WT>, dim3(T), dim3(th), 0, s, (TT*)out, stream, (const TT*)add1, (const TT*)add2, \
-            (const WT*)w, eps, hidden, first)
+            (const WT*)w, eps, hidden, first, alpha, vec, (const WT*)nbias)
   if (dtype == TS_F32 && w_dtype == TS_F32) TS_WN(float, float);
   else if (dtype == TS_BF16 && w_dtype == TS_BF16) TS_WN(bf16, bf16);
   else if (dtype == TS_BF16 && w_dtype == TS_F32) TS_WN(bf16, float);

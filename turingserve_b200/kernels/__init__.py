@@ -68,7 +68,7 @@ class LazyProduct:
 class CudaOps:
     """ctypes front of ``libturingserve_b200.so``."""
 
-    ABI = 10
+    ABI = 11
     UNSUPPORTED = -4            # a kernel's refusal of a shape or layout another kernel takes
 
     def __init__(self, lib_path: str) -> None:
@@ -108,7 +108,7 @@ class CudaOps:
             "ts_decode_step": [P, I, I, P],
             "ts_decode_step_encode_map": [P, P, I, I],
             "ts_poke_status": [I, I, P],
-            "ts_rmsnorm_wide": [P, P, P, P, P, F, I, I, I, I, I, P, I, P, P],
+            "ts_rmsnorm_wide": [P, P, P, P, P, F, I, I, I, I, I, P, I, P, F, P, P, P],
             "ts_activation_parts": [P, P, I, P, I, I, I, I, P],
             "ts_gated_rmsnorm": [P, P, P, I, P, F, I, I, I, I, P],
             "ts_activation": [P, P, ctypes.c_longlong, I, I, P],
@@ -116,16 +116,17 @@ class CudaOps:
             "ts_kv_write_pair": [P, I, I, I, P, P, P, I, I, I, I, I, I, P],
             "ts_attention_diff": [P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, F, F, I, P],
             "ts_attention_diff_mma": [P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, F, F, P, P, I, I, P],
-            "ts_router_topk": [P, P, P, P, I, I, I, I, I, I, I, P],
-            "ts_moe_align": [P, I, I, P, P, P, P, P],
+            "ts_router_topk": [P, P, P, P, I, I, I, I, I, I, I, P, P],
+            "ts_moe_align": [P, I, I, P, P, P, P, I, P],
             "ts_grouped_linear": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
-            "ts_moe_combine": [P, P, P, P, I, I, I, I, P],
+            "ts_moe_combine": [P, P, P, P, I, I, I, I, P, P, P],
             "ts_moe_gather": [P, P, P, P, I, I, I, I, P],
             "ts_delta_prepare": [P, P, I, P, P, P, P, ctypes.c_longlong, P, P, P, I, I, I, I, I, I, F, I, P],
             "ts_delta_scan": [P, P, P, I, P, ctypes.c_longlong, P, P, I, I, I, I, I, I, I, I, P],
             "ts_head_gated_rmsnorm": [P, P, P, I, P, F, I, I, I, I, P],
-            "ts_attention_biased": [P, I, I, P, I, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, P, I, I, P, P, I, P],
-            "ts_attention_biased_mma": [P, I, I, P, I, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, P, I, I, P, P, I, P],
+            "ts_attention_biased": [P, I, I, P, I, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, P, I, I, P, P, I, I, P, P],
+            "ts_attention_biased_mma": [P, I, I, P, I, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, P, I, I, P, P, I, I, P, P],
+            "ts_rope_headnorm_write": [P, I, I, I, P, P, I, I, F, P, P, P, I, I, I, I, I, I, I, P],
             "ts_rms_rows": [P, P, I, I, I, P, F, I, I, P],
             "ts_qk_rownorm_write": [P, I, P, P, F, P, F, I, P, P, P, I, I, I, I, I, I, P],
             "ts_latent_kv_write": [P, I, I, P, F, P, P, F, I, P, P, I, I, I, I, I, P],
@@ -562,10 +563,12 @@ class CudaOps:
         return out
 
     # -- a residual stream in 32-bit ---------------------------------------------------------------------
-    def rmsnorm_stream(self, out, stream, add1, add2, weight, eps: float, first: bool = False) -> None:
-        """stream (float32 [T, h]) += add1 + add2 (either may be None; ``first``: the stream is started
-        from them instead); out = stream / sqrt(mean(stream^2) + eps) * weight, 32-bit, rounded once.
-        ``out`` None: only the sum."""
+    def rmsnorm_stream(self, out, stream, add1, add2, weight, eps: float, first: bool = False, alpha: float = 1.0,
+                       row=None, norm_bias=None) -> None:
+        """stream (float32 [T, h]) += alpha * (add1 + add2) + row (add1, add2 and ``row``, a float32 [h] vector
+        common to all tokens, may be None; ``first``: the stream is started from them instead);
+        out = stream / sqrt(mean(stream^2) + eps) * weight, or with ``norm_bias`` the layer norm
+        (stream - mean) / sqrt(variance + eps) * weight + norm_bias; 32-bit, rounded once.  ``out`` None: only the sum."""
         T, h = stream.shape
         part, splits, bias = None, 0, None
         if isinstance(add1, (LazyProduct, Deferred)) and self.lib.ts_rmsnorm_wide_takes_parts(h):
@@ -579,7 +582,8 @@ class CudaOps:
             dt = add1.dtype if add1 is not None else (add2.dtype if add2 is not None else out.dtype)
         self._check(self.lib.ts_rmsnorm_wide(_ptr(out), _ptr(stream), _ptr(add1), _ptr(add2), _ptr(weight), float(eps),
                                              T, h, 1 if first else 0, _code(dt), _code(weight.dtype), _ptr(part), splits,
-                                             _ptr(bias), self._stream()), "rmsnorm_stream")
+                                             _ptr(bias), float(alpha), _ptr(row), _ptr(norm_bias), self._stream()),
+                    "rmsnorm_stream")
 
     def gated_rmsnorm(self, out, x, gate, weight, eps: float) -> None:
         """out = x / sqrt(mean(x^2) + eps) * weight * sigmoid(gate), x float32 [T, n]; ``gate`` [T, n] in
@@ -725,6 +729,17 @@ class CudaOps:
                                              _ptr(positions), _ptr(freq), float(magnitude), rot_dims, T, H, R,
                                              _code(src.dtype), self._stream()), "rotate_pairs")
 
+    def rope_headnorm_write(self, proj, k_off: int, v_off: int, positions, freq, rot_dims: int, norm_eps, k_cache, v_cache,
+                            slots, H: int, G: int, D: int, V: int, page_size: int) -> None:
+        """``proj`` [T, ...]: q heads in the columns [0, H D), k heads from ``k_off``, value rows from ``v_off``.  Every q and
+        k head has dimension i < rot_dims / 2 turned with dimension i + rot_dims / 2 by position * freq[i] (32-bit) and,
+        with ``norm_eps`` not None, is then divided by its root mean square (eps inside the root, no weight); q in place,
+        k into ``k_cache`` and the value rows into ``v_cache`` at ``slots`` (None: nothing is cached)."""
+        self._check(self.lib.ts_rope_headnorm_write(
+            _ptr(proj), proj.stride(0), k_off, v_off, _ptr(positions), _ptr(freq), int(rot_dims), 0 if norm_eps is None else 1,
+            float(norm_eps or 0.0), _ptr(k_cache), _ptr(v_cache), _ptr(slots), proj.shape[0], H, G, D, V, page_size,
+            _code(proj.dtype), self._stream()), "rope_headnorm_write")
+
     # bfloat16 per-head products with at least this many rows go to the library's batched product
     batched_library_rows = int(os.environ.get("TURINGSERVE_B200_BATCHED_LIBRARY_ROWS", "17"))
 
@@ -745,10 +760,11 @@ class CudaOps:
     biased_decode_splits = int(os.environ.get("TURINGSERVE_B200_BIASED_DECODE_SPLITS", "0"))
 
     def attention_biased(self, out, q, k_cache, v_cache, block_tables, step, KVH: int, page_size: int, scale: float,
-                         softcap: float, slopes, window) -> None:
+                         softcap: float, slopes, window, chunk=None, sinks=None) -> None:
         """out [T, H, Dv] = softmax over the visible keys of cap tanh(q.k scale / cap) - slope_h (i - j), times the
         values; q [T, H, Dk] (views with unit last stride).  ``v_cache`` None: the values are the first Dv columns
-        of the key rows.  ``softcap`` 0: none; ``slopes`` (float32 [H]) None: none; ``window`` None: none.  The keys
+        of the key rows.  ``softcap`` 0: none; ``slopes`` (float32 [H]) None: none; ``window`` None: none; ``chunk`` c:
+        position i sees only j >= floor(i / c) c; ``sinks`` (float32 [H]): exp(sink_h) joins the softmax's denominator.  The keys
         of requests that bring one token are cut over several blocks when the step's longest context is long."""
         T, H, Dk = q.shape
         Dv = out.shape[2]
@@ -757,6 +773,9 @@ class CudaOps:
         B = step.num_requests
         w = 0 if window is None else int(window)
         reach = min(step.max_seq_len, w) if w else step.max_seq_len
+        c = 0 if chunk is None else int(chunk)
+        if c:
+            reach = min(reach, c)
         splits = self.biased_decode_splits
         v_in_k = 1 if v_cache is None else 0
         if (self.use_fast_attention and q.dtype == torch.bfloat16
@@ -786,7 +805,8 @@ class CudaOps:
                     _ptr(out), out.stride(0), out.stride(1), _ptr(q), q.stride(0), q.stride(1), _ptr(k_cache), _ptr(v_cache),
                     block_tables.data_ptr() + 4 * first * width, step.q_start.data_ptr() + 4 * first,
                     step.seq_lens.data_ptr() + 4 * first, count, width, max_q, H, KVH, Dk, Dv, page_size, float(scale),
-                    float(softcap), _ptr(slopes), w, n_splits, _ptr(scratch), _ptr(counters), spread_flag, self._stream())
+                    float(softcap), _ptr(slopes), w, n_splits, _ptr(scratch), _ptr(counters), spread_flag, c, _ptr(sinks),
+                    self._stream())
 
             if spread:
                 rc = launch(0, nd, 1, ms, 1)
@@ -813,21 +833,23 @@ class CudaOps:
             _ptr(out), out.stride(0), out.stride(1), _ptr(q), q.stride(0), q.stride(1), _ptr(k_cache), _ptr(v_cache),
             _ptr(block_tables), _ptr(step.q_start), _ptr(step.seq_lens), B, block_tables.shape[1], step.max_q_len, H, KVH,
             Dk, Dv, page_size, float(scale), float(softcap), _ptr(slopes), w, splits, _ptr(scratch), _ptr(counters),
-            _code(q.dtype), self._stream()), "attention_biased")
+            _code(q.dtype), c, _ptr(sinks), self._stream()), "attention_biased")
 
     # -- routed feed-forward ---------------------------------------------------------------------------------
-    def router_topk(self, idx, weights, x, w_router, softmax: bool, renormalize: bool) -> None:
+    def router_topk(self, idx, weights, x, w_router, softmax: bool, renormalize: bool, correction=None) -> None:
         """idx (int32 [T, top]), weights (float32 [T, top]): the ``top`` experts with the largest router
-        logits w_router (float32 [E, K]) . x, and their scores (sigmoid, or softmax over all experts)."""
+        logits w_router (float32 [E, K]) . x, and their scores (sigmoid, or softmax over all experts).  With
+        ``correction`` (float32 [E]) the choice goes by score + correction; the weights stay the scores."""
         T, top = idx.shape
         E, K = w_router.shape
         self._check(self.lib.ts_router_topk(_ptr(idx), _ptr(weights), _ptr(x), _ptr(w_router), T, E, K, top,
-                                            1 if softmax else 0, 1 if renormalize else 0, _code(x.dtype), self._stream()),
-                    "router_topk")
+                                            1 if softmax else 0, 1 if renormalize else 0, _code(x.dtype), _ptr(correction),
+                                            self._stream()), "router_topk")
 
-    def moe_align(self, idx, E: int):
+    def moe_align(self, idx, E: int, with_tiles: int | None = None):
         """Sorts the (token, choice) pairs of ``idx`` by expert on the device.  Returns (offsets [E + 1],
-        order [P], place [P], tiles): work buffers of this object, valid until the next call."""
+        order [P], place [P], tiles): work buffers of this object, valid until the next call.  ``with_tiles``:
+        only the experts below it get row tiles for the grouped products (the others have no weights)."""
         P = idx.numel()
         dev = idx.device
         rows = self.lib.ts_moe_tile_rows()
@@ -836,7 +858,7 @@ class CudaOps:
         place = self._buffer("moe_place", P, torch.int32, dev, floor=1 << 14)
         tiles = self._buffer("moe_tiles", 1 + 2 * (-(-P // rows) + E), torch.int32, dev, floor=1 << 12)
         self._check(self.lib.ts_moe_align(_ptr(idx), P, E, _ptr(offsets), _ptr(order), _ptr(place), _ptr(tiles),
-                                          self._stream()), "moe_align")
+                                          E if with_tiles is None else int(with_tiles), self._stream()), "moe_align")
         return offsets, order, place, tiles
 
     def grouped_linear(self, out, x, w, order, row_scale, offsets, tiles, top: int, act: str = "none") -> None:
@@ -855,11 +877,13 @@ class CudaOps:
         self._check(self.lib.ts_moe_gather(_ptr(xs), _ptr(x), _ptr(order), _ptr(row_scale), P, top, K, _code(x.dtype),
                                            self._stream()), "moe_gather")
 
-    def moe_combine(self, out, y, place, pair_weights, top: int) -> None:
-        """out[t] = sum over a token's choices r of (pair_weights[t, r] *) y[place[t top + r]] (y float32)."""
+    def moe_combine(self, out, y, place, pair_weights, top: int, x=None, pass_from=None) -> None:
+        """out[t] = sum over a token's choices r of (pair_weights[t, r] *) y[place[t top + r]] (y float32).  With ``x``
+        ([T, N], out's type) and ``pass_from`` (one int32 on the device): a pair sorted to that place or a later
+        one adds x[t] instead of a row of y (experts that return their input)."""
         T, N = out.shape
         self._check(self.lib.ts_moe_combine(_ptr(out), _ptr(y), _ptr(place), _ptr(pair_weights), T, top, N,
-                                            _code(out.dtype), self._stream()), "moe_combine")
+                                            _code(out.dtype), _ptr(x), _ptr(pass_from), self._stream()), "moe_combine")
 
     PAIR_PLAIN, PAIR_GATED = 0, 1
     # The many-row products whose epilogue saves a kernel (gate/up with the activation, q/k/v with rotation and

@@ -15,7 +15,8 @@ PositionEncoding  tables()/apply are private to the mixers that accept it
 Mixer           forward(x, step, cache, state) -> y     cache_need() / state_need() declare memory
 FeedForward     forward(x) -> y                         (mixers and feed-forwards get tensors; they may
                                                          return what ops().linear(..., may_defer=True) gave)
-Block           forward(h, residual, step, cache, state) -> (h, residual)
+Block           forward(h, residual, step, cache, state) -> (h, residual)   (h is whatever the arrangement's own
+                                                         norm takes: a tensor, a product put off, a ``BranchSum``)
 
 ``step`` is a ``StepInputs`` (turingserve_b200.engine.batch): the flat batch on the device.
 """
@@ -48,12 +49,15 @@ class CacheNeed:
     """What a mixer wants from the paged cache: keys and values of ``num_kv_heads`` x ``head_dim``
     per token; ``window`` None keeps every token, an integer keeps the last ``window`` of them.
     ``value_dim``: the width of a value row where it differs from a key row's ``head_dim`` (the
-    group's keys and values are then two tensors instead of one pool)."""
+    group's keys and values are then two tensors instead of one pool).  ``chunk`` c: a position sees only
+    the keys of its own block of c positions (blocks counted from position 0), so tokens before the block of
+    the next position need not be kept."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
     value_dim: int | None = None
+    chunk: int | None = None
 
     @property
     def v_dim(self) -> int:
@@ -101,6 +105,18 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+@dataclass
+class BranchSum:
+    """What a layer whose branches all read one norm's output leaves pending: the branches' outputs (``second``
+    may be None) and the constant their sum is multiplied by on its way into the residual stream.  The norm that
+    follows takes them into the stream in its own kernel.  An embedding on its way into a stream that is about
+    to start has the same form (the rows and their multiplier)."""
+
+    first: Any
+    second: Any = None
+    scale: float = 1.0
+
+
 @dataclass(frozen=True)
 class BuildContext:
     """What every part constructor gets besides its spec."""
@@ -142,7 +158,7 @@ def _load_builtin() -> None:
         _loaded = True
         from turingserve_b200.parts import (  # noqa: F401
             attention, block, capped_attention, delta_rule, diff_attention, gated_mlp, latent_attention, lightning, mlp,
-            rmsnorm, rotary, routed_mlp)
+            rmsnorm, rotary, routed_mlp, sink_attention)
 
 
 def build_block(layer_spec: Any, ctx: BuildContext):

@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 
 from turingserve_b200 import kernels
-from turingserve_b200.parts.base import BuildContext, build, register
+from turingserve_b200.parts.base import BranchSum, BuildContext, build, register
 
 
 class PreNormBlock:
@@ -75,5 +75,41 @@ class StreamBlock:
         return h, residual
 
 
+class ParallelBlock:
+    """One norm, whose output every branch reads, over a residual stream in 32-bit:
+    h = norm(x); x <- x + scale * (mixer(h) + ff(h)).  The add is put off into the norm that follows (the next
+    layer's, or the model's last): the block returns the branches' outputs as a ``BranchSum``.  Roles: ``norm``,
+    ``mixer``, ``feed_forward`` (may be missing) and ``join`` (a ``BranchJoinSpec``: the constant ``scale``).
+    ``inject``: a float32 vector added to every row of the stream before the norm."""
+
+    def __init__(self, spec, ctx: BuildContext) -> None:
+        self.norm = build("norm", spec.norm, ctx)
+        self.mixer = build("mixer", spec.mixer, ctx)
+        self.has_ff = "feed_forward" in spec.roles
+        self.feed_forward = build("feed_forward", spec.feed_forward, ctx) if self.has_ff else None
+        self.scale = float(spec.roles["join"].scale) if "join" in spec.roles else 1.0
+
+    def parts(self) -> dict[str, object]:
+        p = {"norm": self.norm, "mixer": self.mixer}
+        if self.has_ff:
+            p["feed_forward"] = self.feed_forward
+        return p
+
+    def forward(self, h, residual, step, cache, state, inject=None):
+        first = residual is None
+        if first:
+            rows = h.first if isinstance(h, BranchSum) else h
+            residual = torch.empty(rows.shape, dtype=torch.float32, device=rows.device)
+        x = self.norm.forward(h, residual, row=inject, first=first)
+        a = self.mixer.forward(x, step, cache, state)
+        if self.has_ff and isinstance(a, kernels.Deferred):
+            # a product whose partial sums already sit in the work buffer that all such products share: the
+            # feed-forward's last product would write over them, so this one is finished first
+            a = kernels.ops().materialize(a)
+        b = self.feed_forward.forward(x) if self.has_ff else None
+        return BranchSum(a, b, self.scale), residual
+
+
 register("block", "pre_norm", _build_block)
+register("block", "parallel", lambda spec, ctx: ParallelBlock(spec, ctx))
 register("block", "pre_norm_stream", lambda spec, ctx: StreamBlock(spec, ctx))

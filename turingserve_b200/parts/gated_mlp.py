@@ -17,18 +17,25 @@ class GatedMLP(FeedForward):
         self.hidden = ctx.hidden_size
         self.inter = int(spec.intermediate_size)
         self.bias = bool(spec.bias)
+        self.names = tuple(getattr(spec, "names", ("gate_proj.weight", "up_proj.weight", "down_proj.weight")))
+        if self.bias and any(not n.endswith(".weight") for n in self.names):
+            raise ValueError("gated_mlp: biases are named after weights that end in '.weight'")
         self.w_gate_up = self.b_gate_up = self.w_down = self.b_down = None
         self.group = 0
 
     def parameters(self) -> dict[str, ParamSpec]:
-        p = {"gate_proj.weight": ParamSpec((self.inter, self.hidden)),
-             "up_proj.weight": ParamSpec((self.inter, self.hidden)),
-             "down_proj.weight": ParamSpec((self.hidden, self.inter))}
+        g, u, d = self.names
+        p = {g: ParamSpec((self.inter, self.hidden)), u: ParamSpec((self.inter, self.hidden)),
+             d: ParamSpec((self.hidden, self.inter))}
         if self.bias:
-            p["gate_proj.bias"] = ParamSpec((self.inter,))
-            p["up_proj.bias"] = ParamSpec((self.inter,))
-            p["down_proj.bias"] = ParamSpec((self.hidden,))
+            p[self._bias_of(g)] = ParamSpec((self.inter,))
+            p[self._bias_of(u)] = ParamSpec((self.inter,))
+            p[self._bias_of(d)] = ParamSpec((self.hidden,))
         return p
+
+    @staticmethod
+    def _bias_of(weight_name: str) -> str:
+        return weight_name[: -len("weight")] + "bias"
 
     # Gate and up rows are interleaved in blocks of GROUP when the width allows: a 128-row tile of the
     # fused product then holds 64 gates and their 64 ups, and a kernel that computes such a tile can
@@ -44,11 +51,12 @@ class GatedMLP(FeedForward):
 
     def load(self, t: dict[str, torch.Tensor]) -> None:
         self.group = self.GROUP if self.inter % self.GROUP == 0 else 0
-        self.w_gate_up = self._pack(t["gate_proj.weight"], t["up_proj.weight"])
-        self.w_down = t["down_proj.weight"].contiguous()
+        g, u, d = self.names
+        self.w_gate_up = self._pack(t[g], t[u])
+        self.w_down = t[d].contiguous()
         if self.bias:
-            self.b_gate_up = self._pack(t["gate_proj.bias"], t["up_proj.bias"])
-            self.b_down = t["down_proj.bias"].contiguous()
+            self.b_gate_up = self._pack(t[self._bias_of(g)], t[self._bias_of(u)])
+            self.b_down = t[self._bias_of(d)].contiguous()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         ops = kernels.ops()

@@ -40,7 +40,16 @@ class DecoderModel:
                     out[prefix + local] = spec
         for local, spec in self.final_norm.parameters().items():
             out[names.final_norm + local] = spec
+        out.update(self.extra_parameters())
         return out
+
+    def extra_parameters(self) -> dict[str, ParamSpec]:
+        """Checkpoint tensors (by their full names) that belong to the model itself and to none of its parts; a
+        model class that has some overrides this and ``load_extras``."""
+        return {}
+
+    def load_extras(self, tensors: dict[str, torch.Tensor]) -> None:
+        """Receives the tensors ``extra_parameters`` named."""
 
     def load(self, names: TensorNames, tensors: dict[str, torch.Tensor]) -> None:
         """``tensors``: full name -> tensor on the device, already converted."""
@@ -53,6 +62,7 @@ class DecoderModel:
                 part.load({local: tensors[prefix + local] for local in part.parameters()})
         self.final_norm.load({local: tensors[names.final_norm + local]
                               for local in self.final_norm.parameters()})
+        self.load_extras({n: tensors[n] for n in self.extra_parameters()})
 
     # -- what the cache manager has to provide -----------------------------------------------------
     def run_mixer(self, run_index: int):
@@ -67,11 +77,17 @@ class DecoderModel:
         h = h0 = self.embed(step)
         residual = None
         for r, run in enumerate(self.cfg.schedule):
-            if run.add_embedding:
-                h, residual = self.blocks[run.layer].forward(h, residual, step, cache_views[r], states[r], inject=h0)
+            inject = self.injection(run, h0)
+            if inject is not None:
+                h, residual = self.blocks[run.layer].forward(h, residual, step, cache_views[r], states[r], inject=inject)
             else:
                 h, residual = self.blocks[run.layer].forward(h, residual, step, cache_views[r], states[r])
         return self.final_norm.forward(h, residual)
+
+    def injection(self, run, h0):
+        """What is added to the stream before ``run`` (None: nothing): the step's embedding rows where the schedule
+        asks for them.  A model class with vectors of its own for the passes of a repeated span overrides this."""
+        return h0 if run.add_embedding else None
 
     def embed(self, step) -> torch.Tensor:
         """The rows of the embedding table for the step's token ids, [T, hidden].  A model class that

@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 
 from turingserve_b200 import kernels
-from turingserve_b200.parts.base import BuildContext, Norm, ParamSpec, register
+from turingserve_b200.parts.base import BranchSum, BuildContext, Norm, ParamSpec, register
 
 
 class RMSNorm(Norm):
@@ -62,5 +62,42 @@ class StreamRMSNorm(Norm):
         return out
 
 
+class StreamLayerNorm(Norm):
+    """The layer norm of a residual stream kept in 32-bit whatever the engine's type.  ``forward(x, stream)`` first
+    takes what is pending into ``stream`` in place, stream += scale * (a + b) + row, where ``x`` is a tensor (scale 1)
+    or a ``BranchSum`` (the outputs of a layer's branches and the constant they are multiplied by) and ``row`` a
+    float32 vector common to all tokens; then returns (stream - mean) / sqrt(variance + eps) * weight + bias in the
+    engine's type (32-bit arithmetic, one rounding).  ``first``: ``stream`` is started instead of added to."""
+
+    def __init__(self, spec, ctx: BuildContext) -> None:
+        self.eps = float(spec.eps)
+        self.size = ctx.hidden_size
+        self.dtype = ctx.dtype
+        self.weight_name, self.bias_name = str(spec.weight_name), str(spec.bias_name)
+        if self.weight_name == self.bias_name:
+            raise ValueError("layernorm_stream: weight and bias need two tensor names")
+        self.weight: torch.Tensor | None = None
+        self.bias: torch.Tensor | None = None
+
+    def parameters(self) -> dict[str, ParamSpec]:
+        return {self.weight_name: ParamSpec((self.size,), compute_dtype=False, init="ones"),
+                self.bias_name: ParamSpec((self.size,), compute_dtype=False, init="zeros")}
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        # both in 32-bit: the kernel reads them as one type, and the norm's arithmetic is 32-bit anyway
+        self.weight = tensors[self.weight_name].float().contiguous()
+        self.bias = tensors[self.bias_name].float().contiguous()
+
+    def forward(self, x, residual: torch.Tensor | None = None, row=None, first: bool = False) -> torch.Tensor:
+        if residual is None:
+            raise ValueError("the stream norm needs the 32-bit stream it adds to")
+        a, b, scale = (x.first, x.second, x.scale) if isinstance(x, BranchSum) else (x, None, 1.0)
+        out = torch.empty(residual.shape, dtype=self.dtype, device=residual.device)
+        kernels.ops().rmsnorm_stream(out, residual, a, b, self.weight, self.eps, first, alpha=scale, row=row,
+                                     norm_bias=self.bias)
+        return out
+
+
 register("norm", "rmsnorm", RMSNorm)
+register("norm", "layernorm_stream", StreamLayerNorm)
 register("norm", "rmsnorm_stream", StreamRMSNorm)

@@ -55,5 +55,20 @@ class PairRotaryEncoding:
         self.freq = f.to(torch.float32).to(ctx.device).contiguous()
 
 
+class HalfRotaryEncoding:
+    """Rotation of the pairs (i, i + dims / 2) without a table over positions: the kernels take the angle as
+    position * ``freq[i]`` in 32-bit.  ``freq`` is float32 [dims / 2] on the device, base^(-2i/dims) worked out in
+    double and rounded once."""
+
+    def __init__(self, spec, ctx: BuildContext) -> None:
+        self.dims = int(spec.dims)
+        if self.dims % 2 or self.dims < 0:
+            raise ValueError("the rotated dimensions come in pairs")
+        i = torch.arange(self.dims // 2, dtype=torch.float64)
+        f = float(spec.base) ** (-2.0 * i / max(self.dims, 1))
+        self.freq = f.to(torch.float32).to(ctx.device).contiguous()
+
+
 register("position", "rope", RotaryEncoding)
+register("position", "rope_half", HalfRotaryEncoding)
 register("position", "yarn_pairs", PairRotaryEncoding)

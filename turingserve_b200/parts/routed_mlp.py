@@ -1,5 +1,8 @@
 """Routed feed-forward: every token goes through the ``top_k`` of ``num_experts`` small feed-forwards
-down_e(act(up_e(.))) whose router scores are largest.
+down_e(act(up_e(.))), or gated ones down_e(act(gate_e(.)) * up_e(.)), whose router scores are largest.
+A learned correction may enter the choice (score + correction) without entering the weights.  The router may have
+more outputs than there are experts with tensors: the outputs behind them are experts that return their input,
+which cost no product (their pairs are sorted behind the others and the sum takes the token's own row for them).
 
 Router logits and scores are 32-bit.  The (token, choice) pairs are sorted by expert on the device and the
 two products run over the sorted groups; the chosen score multiplies the expert's input (``weight_on``
@@ -29,7 +32,7 @@ class RoutedMLP(FeedForward):
     def __init__(self, spec, ctx: BuildContext) -> None:
         self.hidden = ctx.hidden_size
         self.E, self.top, self.inter = int(spec.num_experts), int(spec.top_k), int(spec.intermediate_size)
-        if not 1 <= self.top <= self.E:
+        if self.top < 1 or self.E < 0:
             raise ValueError(f"routed_mlp: top {self.top} of {self.E} experts")
         if spec.activation not in ACTIVATIONS:
             raise ValueError(f"routed_mlp: activation {spec.activation!r} has no kernel")
@@ -37,18 +40,39 @@ class RoutedMLP(FeedForward):
             raise ValueError(f"routed_mlp: scoring {spec.scoring!r} / weight_on {spec.weight_on!r}")
         self.activation, self.softmax = spec.activation, spec.scoring == "softmax"
         self.renormalize, self.on_input = bool(spec.renormalize), spec.weight_on == "input"
-        self.w_router = self.w_up = self.w_down = None
+        self.gated, self.has_correction = bool(getattr(spec, "gated", False)), bool(getattr(spec, "correction", False))
+        self.identity = int(getattr(spec, "identity", 0))
+        if self.identity < 0:
+            raise ValueError(f"routed_mlp: {self.identity} identity experts")
+        if self.gated and self.activation != "silu":
+            raise ValueError(f"routed_mlp: gated experts with activation {self.activation!r} have no kernel")
+        if self.identity and self.on_input:
+            raise ValueError("routed_mlp: experts that return their input are weighted on the output")
+        self.outputs = self.E + self.identity           # what the router scores
+        if self.top > self.outputs:
+            raise ValueError(f"routed_mlp: top {self.top} of {self.outputs} router outputs")
+        self.w_router = self.w_up = self.w_down = self.correction = None
 
     def parameters(self) -> dict[str, ParamSpec]:
-        p = {"router": ParamSpec((self.E, self.hidden), compute_dtype=False)}
+        p = {"router": ParamSpec((self.outputs, self.hidden), compute_dtype=False)}
+        if self.has_correction:
+            p["correction"] = ParamSpec((self.outputs,), compute_dtype=False, init="zeros")
         for e in range(self.E):
+            if self.gated:
+                p[f"e{e}.gate"] = ParamSpec((self.inter, self.hidden))
             p[f"e{e}.up"] = ParamSpec((self.inter, self.hidden))
             p[f"e{e}.down"] = ParamSpec((self.hidden, self.inter))
         return p
 
     def load(self, t: dict[str, torch.Tensor]) -> None:
         self.w_router = t["router"].float().contiguous()
-        self.w_up = torch.stack([t[f"e{e}.up"] for e in range(self.E)]).contiguous()
+        if self.has_correction:
+            self.correction = t["correction"].float().contiguous()
+        if self.E == 0:
+            return
+        # gated experts: an expert's gate rows, then its up rows, in one product
+        ups = [torch.cat([t[f"e{e}.gate"], t[f"e{e}.up"]], dim=0) if self.gated else t[f"e{e}.up"] for e in range(self.E)]
+        self.w_up = torch.stack(ups).contiguous()
         self.w_down = torch.stack([t[f"e{e}.down"] for e in range(self.E)]).contiguous()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -56,10 +80,21 @@ class RoutedMLP(FeedForward):
         T, top = x.shape[0], self.top
         idx = torch.empty((T, top), dtype=torch.int32, device=x.device)
         weights = torch.empty((T, top), dtype=torch.float32, device=x.device)
-        ops.router_topk(idx, weights, x, self.w_router, self.softmax, self.renormalize)
-        offsets, order, place, tiles = ops.moe_align(idx, self.E)
-        a = torch.empty((T * top, self.inter), dtype=x.dtype, device=x.device)
+        ops.router_topk(idx, weights, x, self.w_router, self.softmax, self.renormalize, self.correction)
+        out = torch.empty((T, self.hidden), dtype=x.dtype, device=x.device)
+        if self.identity:
+            # the pairs of the experts with tensors are sorted first; the others' output is the token's own row
+            offsets, order, place, tiles = ops.moe_align(idx, self.outputs, self.E)
+            passing = dict(x=x, pass_from=offsets[self.E:self.E + 1])
+        else:
+            offsets, order, place, tiles = ops.moe_align(idx, self.E)
+            passing = {}
         y = torch.empty((T * top, self.hidden), dtype=torch.float32, device=x.device)
+        if self.E == 0:
+            ops.moe_combine(out, y, place, weights, top, **passing)
+            return out
+        up_width = (2 if self.gated else 1) * self.inter
+        a = torch.empty((T * top, up_width), dtype=x.dtype, device=x.device)
         # the experts' input rows in sorted order, weighted and rounded once (the products then read plain rows)
         xs = torch.empty((T * top, self.hidden), dtype=x.dtype, device=x.device)
         ops.moe_gather(xs, x, order, weights if self.on_input else None, top)
@@ -69,17 +104,33 @@ class RoutedMLP(FeedForward):
                 lo, hi = bounds[e], bounds[e + 1]
                 if hi > lo:
                     ops.linear(a[lo:hi], xs[lo:hi], self.w_up[e])
-            ops.activation(a, a, self.activation)
+            a = self._activate(a, bounds[self.E])
             for e in range(self.E):
                 lo, hi = bounds[e], bounds[e + 1]
                 if hi > lo:
                     ops.linear(y[lo:hi], a[lo:hi], self.w_down[e])
+        elif self.gated:
+            ops.grouped_linear(a, xs, self.w_up, None, None, offsets, tiles, 1)
+            a = self._activate(a, T * top)
+            ops.grouped_linear(y, a, self.w_down, None, None, offsets, tiles, 1)
         else:
             ops.grouped_linear(a, xs, self.w_up, None, None, offsets, tiles, 1, self.activation)
             ops.grouped_linear(y, a, self.w_down, None, None, offsets, tiles, 1)
-        out = torch.empty((T, self.hidden), dtype=x.dtype, device=x.device)
-        ops.moe_combine(out, y, place, None if self.on_input else weights, top)
+        ops.moe_combine(out, y, place, None if self.on_input else weights, top, **passing)
         return out
+
+    def _activate(self, a: torch.Tensor, rows: int) -> torch.Tensor:
+        """The first ``rows`` rows of the experts' first product through the activation (the rows behind them belong
+        to experts without tensors and hold nothing); gated experts: act(gate) * up, half as wide."""
+        ops = kernels.ops()
+        if not self.gated:
+            if rows:
+                ops.activation(a[:rows], a[:rows], self.activation)
+            return a
+        g = torch.empty((a.shape[0], self.inter), dtype=a.dtype, device=a.device)
+        if rows:
+            ops.silu_mul(g[:rows], a[:rows], 0)
+        return g
 
 
 register("feed_forward", "routed_mlp", RoutedMLP)
