@@ -836,6 +836,135 @@ def pizunex_kernels(ops, z: dict, pk: dict, T: int, B: int, ctx: int, page: int)
     return out
 
 
+# ---- Vofinex (parallel layers on one layer norm, attention in blocks of positions with a sink, q and k rotated by
+# halves and normed head by head, gated experts beside identity outputs) at layer sizes of real models, next to Komirax
+# layers of the same width and weight count ---------------------------------------------------------------------------
+VOFINEX_SIZES = {
+    # width; heads, kv heads, head width (keys and values), rotated dimensions, block of positions; gated dense ff;
+    # experts with tensors, identity outputs, top, gated expert ff (three matrices: two thirds of Komirax's widths)
+    "1.5b": dict(width=1536, heads=12, kv_heads=2, dim=128, rot=64, size=1024, ff=8960, experts=8, identity=4, top=4, eff=1792,
+                 beside="1.5b"),
+    "7b": dict(width=3584, heads=28, kv_heads=4, dim=128, rot=64, size=1024, ff=18944, experts=8, identity=4, top=4, eff=4736,
+               beside="7b"),
+}
+
+
+def vofinex_config(z: dict, groups: int, vocab: int):
+    """``groups`` times four parallel layers: (attention, dense), (attention, routed), (attention, routed), (attention,
+    dense); the whole stack is one span that runs once (its vector is added to the stream)."""
+    from turingserve_b200.models.vofinex import make_config
+    att = {"type": "attention", "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                                          "scale": z["dim"] ** -0.5, "mask": {"size": z["size"]},
+                                          "rot": {"base": 500000.0, "dims": z["rot"]}}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["eff"]},
+           "router": {"experts": z["experts"], "identity": z["identity"], "top": z["top"]}}
+    four = [{**att, "mlp": dense}, {**att, "mlp": moe}, {**att, "mlp": moe}, {**att, "mlp": dense}]
+    return make_config(width=z["width"], vocab=vocab, layers=four * groups, eps=1e-6, residual_mult=0.5, embedding_scale=4.0,
+                       logit_scale=0.5, loop={"start": 0, "stop": 4 * groups, "times": 1})
+
+
+def vofinex_kernels(ops, z: dict, pk: dict, T: int, B: int, ctx: int, page: int) -> dict:
+    """Each kernel of the new mechanisms alone: a portion of T tokens and B single tokens at context ``ctx``."""
+    import torch
+    from types import SimpleNamespace
+    dev = torch.device("cuda", 0)
+    big = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    flush = lambda: big.fill_(1)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    out = {}
+    hbm = pk["hbm_gbs"] * 1e9
+    bf = torch.bfloat16
+    H, G, D, W, size, rot = z["heads"], z["kv_heads"], z["dim"], z["width"], z["size"], z["rot"]
+
+    # the stream's layer norm: two branch outputs and the pass vector into the 32-bit stream, then the norm
+    for name, rows in (("prefill", T), ("decode", B)):
+        stream = torch.randn(rows, W, device=dev)
+        a_, b_ = torch.randn(rows, W, device=dev).to(bf), torch.randn(rows, W, device=dev).to(bf)
+        w_, nb, row = torch.ones(W, device=dev), torch.zeros(W, device=dev), torch.zeros(W, device=dev)
+        o = torch.empty(rows, W, dtype=bf, device=dev)
+        ms = timed(lambda: ops.rmsnorm_stream(o, stream, a_, b_, w_, 1e-6, False, alpha=0.5, row=row, norm_bias=nb), flush)
+        ms_r = timed(lambda: ops.rmsnorm_stream(o, stream, a_, None, w_, 1e-6, False), flush)
+        byts = rows * W * (4 + 4 + 2 + 2 + 2.0)
+        out[f"stream_layer_norm_{name}"] = {"us": round(ms * 1e3, 1), "frac_of_hbm": round(byts / (ms / 1e3) / hbm, 3),
+                                            "beside_rms_norm_us": round(ms_r * 1e3, 1),
+                                            "beside_frac_of_hbm": round(rows * W * 12.0 / (ms_r / 1e3) / hbm, 3)}
+
+    pages = B * (-(-(ctx + 1) // page)) + -(-T // page) + 2
+    width = -(-max(ctx + 1, T) // page)
+    kc = torch.randn(pages, G, page, D, device=dev).to(bf)
+    vc = torch.randn(pages, G, page, D, device=dev).to(bf)
+    # rotation by halves, unit heads, cache write
+    freq = (500000.0 ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot)).float().to(dev)
+    for name, rows in (("prefill", T), ("decode", B)):
+        proj = torch.randn(rows, (H + 2 * G) * D, device=dev).to(bf)
+        pos = i32(list(range(rows)))
+        slots = i32(list(range(page, page + rows)))
+        ms = timed(lambda: ops.rope_headnorm_write(proj, H * D, (H + G) * D, pos, freq, rot, 1e-6, kc, vc, slots, H, G, D, D, page), flush)
+        byts = rows * (2 * H * D + 2 * 2 * G * D) * 2.0
+        out[f"rotate_norm_write_{name}"] = {"us": round(ms * 1e3, 1), "frac_of_hbm": round(byts / (ms / 1e3) / hbm, 3)}
+
+    # attention in blocks with a sink
+    sinks = torch.zeros(H, device=dev)
+    for name, reqs, per, seq in (("prefill", 1, T, T), ("decode", B, 1, ctx + 1)):
+        rows = reqs * per
+        q = torch.randn(rows, H, D, device=dev).to(bf)
+        o = torch.empty(rows, H, D, dtype=bf, device=dev)
+        step = SimpleNamespace(q_start=i32([i * per for i in range(reqs + 1)]), seq_lens=i32([seq] * reqs), num_requests=reqs,
+                               num_decode=reqs if per == 1 else 0, max_q_len=per, max_seq_len=seq)
+        bt = torch.zeros(reqs, width, dtype=torch.int32, device=dev)
+        n = -(-seq // page)
+        for r in range(reqs):
+            bt[r, :n] = torch.arange(1 + r * n, 1 + (r + 1) * n, dtype=torch.int32, device=dev)
+        for tag, c in (("", size), ("_no_blocks", None)):
+            ms = timed(lambda: ops.attention_biased(o, q, kc, vc, bt, step, G, page, D ** -0.5, 0.0, None, None, chunk=c,
+                                                    sinks=sinks), flush)
+            seen = sum(i % c + 1 if c else i + 1 for i in range(seq - per, seq))       # keys a request's queries see
+            flops = 4.0 * D * H * seen * reqs
+            held = min(seq, (seq - 1) % c + 1 + (per - 1 if per > 1 else 0)) if c else seq
+            byts = reqs * held * G * 2 * D * 2.0 + rows * H * D * 4.0
+            out[f"sink_attention{tag}_{name}"] = {"us": round(ms * 1e3, 1), "tflops": round(flops / ms / 1e9, 1),
+                                                  "frac_of_bf16": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 3),
+                                                  "frac_of_hbm": round(byts / (ms / 1e3) / hbm, 3)}
+
+    # the routed feed-forward: router (softmax, correction) + sort, gather, gate/up product, activation, down product, sum
+    E, ident, top, ff = z["experts"], z["identity"], z["top"], z["eff"]
+    w_up = (torch.randn(E, 2 * ff, W, device=dev) * 0.02).to(bf)
+    w_down = (torch.randn(E, W, ff, device=dev) * 0.02).to(bf)
+    wr = torch.randn(E + ident, W, device=dev) * 0.05
+    corr = torch.randn(E + ident, device=dev) * 0.01
+    for name, rows in (("prefill", T), ("decode", B)):
+        x = torch.randn(rows, W, device=dev).to(bf)
+        idx = torch.empty(rows, top, dtype=torch.int32, device=dev)
+        wts = torch.empty(rows, top, device=dev)
+        a_ = torch.empty(rows * top, 2 * ff, dtype=bf, device=dev)
+        g_ = torch.empty(rows * top, ff, dtype=bf, device=dev)
+        y = torch.zeros(rows * top, W, device=dev)
+        o = torch.empty(rows, W, dtype=bf, device=dev)
+        ops.router_topk(idx, wts, x, wr, True, False, corr)
+        offsets, order, place, tiles = ops.moe_align(idx, E + ident, E)
+        real = int(offsets[E])                                   # pairs that go to experts with tensors
+        ms_r = timed(lambda: (ops.router_topk(idx, wts, x, wr, True, False, corr), ops.moe_align(idx, E + ident, E)), flush)
+        xs = torch.empty(rows * top, W, dtype=bf, device=dev)
+        ms_g = timed(lambda: ops.moe_gather(xs, x, order, None, top), flush)
+        ms_u = timed(lambda: ops.grouped_linear(a_, xs, w_up, None, None, offsets, tiles, 1), flush)
+        ms_a = timed(lambda: ops.silu_mul(g_, a_, 0), flush)
+        ms_d = timed(lambda: ops.grouped_linear(y, g_, w_down, None, None, offsets, tiles, 1), flush)
+        ms_c = timed(lambda: ops.moe_combine(o, y, place, wts, top, x=x, pass_from=offsets[E:E + 1]), flush)
+        flops_u, flops_d = 4.0 * real * ff * W, 2.0 * real * ff * W
+        used = min(E, max(1, real))
+        out[f"routed_ff_{name}"] = {
+            "pairs_with_tensors": real, "pairs": rows * top,
+            "router_and_sort_us": round(ms_r * 1e3, 1), "gather_us": round(ms_g * 1e3, 1), "up_us": round(ms_u * 1e3, 1),
+            "activation_us": round(ms_a * 1e3, 1), "down_us": round(ms_d * 1e3, 1), "sum_us": round(ms_c * 1e3, 1),
+            "up_tflops": round(flops_u / ms_u / 1e9, 1), "down_tflops": round(flops_d / ms_d / 1e9, 1),
+            "up_frac_of_bf16": round(flops_u / (ms_u / 1e3) / (pk["bf16_tflops"] * 1e12), 3),
+            "down_frac_of_bf16": round(flops_d / (ms_d / 1e3) / (pk["bf16_tflops"] * 1e12), 3),
+            "up_frac_of_hbm": round(used * 2 * ff * W * 2.0 / (ms_u / 1e3) / hbm, 3),
+            "down_frac_of_hbm": round(used * ff * W * 2.0 / (ms_d / 1e3) / hbm, 3)}
+    return out
+
+
 def run_design(a) -> dict:
     """``--design komirax``: prefill and decode throughput of Komirax layers beside Qwen2 layers of the same
     width and count (random weights, bfloat16, through the step function), and each new kernel alone."""
@@ -892,6 +1021,29 @@ def run_design(a) -> dict:
     for name in a.design_sizes.split(","):
         groups = a.layers // 4 if a.layers else 2
         ctx_len = max(ctx + warmup + steps + 64, T + 64)
+        if a.design == "vofinex":
+            # beside Komirax layers of the same width and weight count, the closest design the engine has (a 32-bit
+            # stream, an attention with key and value widths of its own, dense and routed feed-forwards)
+            z = VOFINEX_SIZES[name]
+            eng = build_engine_on_device(f"vofinex-{name}", 4 * groups, ctx_len=ctx_len, page=page, max_seqs=B,
+                                         max_tokens=max(T, ctx), graph_sizes=(B,), mcfg=vofinex_config(z, groups, vocab))
+            ours = measure(eng)
+            del eng
+            torch.cuda.empty_cache()
+            eng = build_engine_on_device(f"komirax-{z['beside']}", 4 * groups, ctx_len=ctx_len, page=page, max_seqs=B,
+                                         max_tokens=max(T, ctx), graph_sizes=(B,),
+                                         mcfg=komirax_config(KOMIRAX_SIZES[z["beside"]], groups, vocab))
+            beside = measure(eng)
+            del eng
+            torch.cuda.empty_cache()
+            entry = {"layers": 4 * groups, "width": z["width"], "vofinex": ours, "beside": f"komirax-{z['beside']}", "komirax": beside,
+                     "prefill_ratio": round(ours["prefill_tok_s"] / beside["prefill_tok_s"], 3),
+                     "decode_ratio": round(ours["decode_tok_s"] / beside["decode_tok_s"], 3)}
+            if "kernels" in a.phases.split(","):
+                entry["kernels"] = vofinex_kernels(ops, z, pk, T, B, ctx, page)
+                entry["komirax_kernels"] = komirax_kernels(ops, KOMIRAX_SIZES[z["beside"]], pk, T, B, ctx, page)
+            result["sizes"][name] = entry
+            continue
         if a.design == "pizunex":
             # beside Komirax layers of the same width, the closest design the engine has (a 32-bit stream, a recurrent
             # mixer with a matrix state, an attention of its own, feed-forwards without a gate)
@@ -1021,7 +1173,7 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--phases", default="prefill,decode,points,e2e,kernels,mixed",
                     help="which measurements to run (decode always runs); fewer for a profiler capture")
-    ap.add_argument("--design", default="", choices=["", "komirax", "pizunex"],
+    ap.add_argument("--design", default="", choices=["", "komirax", "pizunex", "vofinex"],
                     help="instead of the default workload: layers of this design beside layers of the closest other one (Komirax "
                          "beside Qwen2, Pizunex beside Komirax) at the same width "
                          "(prefill and decode throughput, and each of the design's kernels alone)")
