@@ -902,7 +902,12 @@ def vofinex_kernels(ops, z: dict, pk: dict, T: int, B: int, ctx: int, page: int)
         slots = i32(list(range(page, page + rows)))
         ms = timed(lambda: ops.rope_headnorm_write(proj, H * D, (H + G) * D, pos, freq, rot, 1e-6, kc, vc, slots, H, G, D, D, page), flush)
         byts = rows * (2 * H * D + 2 * 2 * G * D) * 2.0
-        out[f"rotate_norm_write_{name}"] = {"us": round(ms * 1e3, 1), "frac_of_hbm": round(byts / (ms / 1e3) / hbm, 3)}
+        # beside it the rotation by a table and cache write of the Qwen2 layers (full heads, no norm) on the same rows
+        cos, sin = torch.ones(rows, D // 2, device=dev), torch.zeros(rows, D // 2, device=dev)
+        ms_q = timed(lambda: ops.rope_kv_write(proj, pos, cos, sin, H, G, D, D, kc, vc, slots, page), flush)
+        out[f"rotate_norm_write_{name}"] = {"us": round(ms * 1e3, 1), "frac_of_hbm": round(byts / (ms / 1e3) / hbm, 3),
+                                            "beside_table_rotation_us": round(ms_q * 1e3, 1),
+                                            "beside_frac_of_hbm": round(byts / (ms_q / 1e3) / hbm, 3)}
 
     # attention in blocks with a sink
     sinks = torch.zeros(H, device=dev)

@@ -117,6 +117,37 @@ def test_rotation_by_halves_then_unit_heads_into_the_cache(ops, dtype, H, G, D, 
     assert torch.equal(again[:, :H * D], proj[:, :H * D])
 
 
+@pytest.mark.parametrize("T", [1, 5, 8, 33, 100])
+@pytest.mark.parametrize("H,G,D,V,rot", [(6, 1, 128, 80, 32), (12, 2, 128, 128, 64), (4, 2, 64, 64, 64), (3, 3, 24, 40, 24)])
+def test_a_projection_left_unreduced_is_finished_by_the_rotation_kernel(ops, T, H, G, D, V, rot):
+    """bfloat16, a few tokens: the q/k/v product leaves the partial sums of its cuts along K and the kernel that rotates
+    sums them on the way: the same bits in q and in the cache as the finished product followed by the kernel."""
+    from turingserve_b200 import kernels
+    g = torch.Generator(device=DEV).manual_seed(T + D)
+    K, page = 1536, 16
+    N = (H + G) * D + G * V
+    x = torch.randn(T, K, generator=g, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g, device=DEV) * 0.05).to(torch.bfloat16)
+    freq = (500000.0 ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot)).float().to(DEV)
+    pos = i32([700 + 3 * t for t in range(T)])
+    slots = i32([page + 2 * t for t in range(T)])
+    results = []
+    for defer in (False, True):
+        out = torch.zeros(T, N, dtype=torch.bfloat16, device=DEV)
+        k_cache = torch.zeros(2 + 2 * T // page + 1, G, page, D, dtype=torch.bfloat16, device=DEV)
+        v_cache = torch.zeros(2 + 2 * T // page + 1, G, page, V, dtype=torch.bfloat16, device=DEV)
+        proj = ops.linear(out, x, w, may_defer=defer, lazy=False)
+        if defer and N % 8 == 0:
+            assert isinstance(proj, kernels.Deferred)
+        proj = ops.rope_headnorm_write(proj, H * D, (H + G) * D, pos, freq, rot, 1e-6, k_cache, v_cache, slots, H, G, D, V, page)
+        results.append((proj[:, :H * D].clone(), k_cache, v_cache))
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
+    want = plain.unit_rms(plain.rotate_half((x.double() @ w.double().T).cpu()[:, :H * D].view(T, H, D),
+                                            pos.cpu(), rot, 500000.0), 1e-6)
+    assert torch.allclose(results[1][0].double().cpu().view(T, H, D), want, rtol=3e-2, atol=3e-2)
+
+
 def test_rotation_keeps_scores_a_function_of_distance(ops):
     """The same q and k rows at positions (p + 7, p) for p = 0, 50, 3000: equal scores after rotation (no norm)."""
     H = G = 1

@@ -80,7 +80,7 @@ class TwinOps:
         paged_attention(out, qkv, k_cache, v_cache, block_tables, step.q_start, step.seq_lens,
                         H, KVH, D, page_size, scale, window)
 
-    def linear(self, out, x, w, bias=None, rows=None, may_defer=False):
+    def linear(self, out, x, w, bias=None, rows=None, may_defer=False, lazy=True):
         if rows is not None:
             x = x[rows.long()]
         y = F.linear(x.float(), w.float(), None if bias is None else bias.float())
@@ -421,13 +421,14 @@ def _rope_headnorm_write(self, proj, k_off, v_off, positions, freq, rot_dims, no
 
     proj[:, :H * D] = turn(q).reshape(T, H * D).to(proj.dtype)
     if slots is None:
-        return
+        return proj
     k = turn(k).to(proj.dtype)
     v = proj[:, v_off:v_off + G * V].view(T, G, V)
     for t, slot in enumerate(slots.tolist()):
         if slot >= 0:
             k_cache[slot // page_size, :, slot % page_size] = k[t]
             v_cache[slot // page_size, :, slot % page_size] = v[t]
+    return proj
 
 
 def _attention_biased(self, out, q, k_cache, v_cache, block_tables, step, KVH, page_size, scale, softcap, slopes, window,

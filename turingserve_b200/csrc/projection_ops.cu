@@ -300,6 +300,115 @@ rope_headnorm_write_kernel(T* __restrict__ proj, int stride, int k_off, int v_of
   }
 }
 
+// The same for bfloat16 rows whose heads are multiples of 8 wide and start on 16-byte boundaries: a lane brings 8
+// neighbouring columns with one 16-byte load, the rotation and the sum of squares run on the 32-bit copy in shared
+// memory (the same operations in the same order as above: the same bits), and 8 columns leave with one store.
+__device__ __forceinline__ void bf16x8_to_f(const uint4& v, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 t = __bfloat1622float2(h[j]);
+    f[2 * j] = t.x;
+    f[2 * j + 1] = t.y;
+  }
+}
+
+__global__ void __launch_bounds__(RHN_WARPS * 32)
+rope_headnorm_write_vec_kernel(bf16* __restrict__ proj, int stride, int k_off, int v_off, const int* __restrict__ positions,
+                               const float* __restrict__ freq, int rot_dims, int norm, float eps, bf16* __restrict__ k_cache,
+                               bf16* __restrict__ v_cache, const int* __restrict__ slots, int H, int G, int D, int V, int page,
+                               const float* __restrict__ part, int splits) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float rhn_s[];
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int head = blockIdx.y * RHN_WARPS + warp;
+  const int slot = slots != nullptr ? slots[t] : -1;
+  bf16* row = proj + (size_t)t * stride;
+  // `part` set: the projection arrives unreduced, [splits, T, stride] partial sums; a column's value is their sum in
+  // ascending order rounded to bfloat16, as the product's own last pass would have left it in `proj`
+  const size_t split_stride = (size_t)gridDim.x * stride;
+  const float* prow = part != nullptr ? part + (size_t)t * stride : nullptr;
+  if (head < H + G) {
+    float* x = rhn_s + warp * D;
+    const int col0 = head < H ? head * D : k_off + (head - H) * D;
+    bf16* src = row + col0;
+    if (prow == nullptr) {
+      for (int c = lane * 8; c < D; c += 256) bf16x8_to_f(*reinterpret_cast<const uint4*>(src + c), x + c);
+    } else {
+      for (int c = lane * 8; c < D; c += 256) {
+        float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int sp = 0; sp < splits; ++sp) {
+          const float4* p4 = reinterpret_cast<const float4*>(prow + sp * split_stride + col0 + c);
+          const float4 a = p4[0], b = p4[1];
+          f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
+          f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[c + j] = round_to<bf16>(f[j]);
+      }
+    }
+    __syncwarp();
+    const float pos = (float)positions[t];
+    const int half = rot_dims / 2;
+    float ss = 0.f;
+    for (int i = lane; i < half; i += 32) {
+      float sn, cs;
+      sincosf(pos * freq[i], &sn, &cs);
+      const float u = x[i], v = x[i + half];
+      const float a = u * cs - v * sn, b = v * cs + u * sn;
+      x[i] = a;
+      x[i + half] = b;
+      ss += a * a + b * b;
+    }
+    for (int i = rot_dims + lane; i < D; i += 32) {
+      const float v = x[i];
+      ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    __syncwarp();
+    const float r = norm ? 1.f / sqrtf(ss / (float)D + eps) : 1.f;
+    bf16* dst = src;
+    if (head >= H) {
+      dst = nullptr;
+      if (slot >= 0) {
+        const size_t pg = slot / page, off = slot % page;
+        dst = k_cache + ((pg * G + (head - H)) * page + off) * D;
+      }
+    }
+    if (dst != nullptr)
+      for (int c = lane * 8; c < D; c += 256) {
+        uint4 o;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) h[j] = __halves2bfloat162(from_f<bf16>(x[c + 2 * j] * r), from_f<bf16>(x[c + 2 * j + 1] * r));
+        *reinterpret_cast<uint4*>(dst + c) = o;
+      }
+  }
+  if (blockIdx.y == 0 && slot >= 0 && v_cache != nullptr) {
+    const size_t pg = slot / page, off = slot % page;
+    if (prow != nullptr) {
+      for (int i = threadIdx.x; i < G * V; i += blockDim.x) {
+        float f = 0.f;
+        for (int sp = 0; sp < splits; ++sp) f += prow[sp * split_stride + v_off + i];
+        const int g = i / V, d = i % V;
+        v_cache[((pg * G + g) * page + off) * V + d] = from_f<bf16>(f);
+      }
+    } else if (V % 8 == 0 && v_off % 8 == 0 && !((uintptr_t)v_cache & 15)) {
+      for (int i = threadIdx.x * 8; i < G * V; i += blockDim.x * 8) {
+        const int g = i / V, d = i % V;
+        *reinterpret_cast<uint4*>(v_cache + ((pg * G + g) * page + off) * V + d) = *reinterpret_cast<const uint4*>(row + v_off + i);
+      }
+    } else {
+      for (int i = threadIdx.x; i < G * V; i += blockDim.x) {
+        const int g = i / V, d = i % V;
+        v_cache[((pg * G + g) * page + off) * V + d] = row[v_off + i];
+      }
+    }
+  }
+}
+
 int threads_for_row(int n) { return n >= 2048 ? 512 : (n >= 512 ? 256 : 128); }
 
 }  // namespace
@@ -361,10 +470,21 @@ TS_API int ts_rotate_pairs(void* dst, int dst_ts, int dst_hs, const void* src, i
 
 // proj [T, stride]: q heads in columns [0, H D), k heads in [k_off, k_off + G D), value rows in [v_off, v_off + G V).
 // freq: 32-bit [rot_dims / 2].  k_cache [pages, G, page, D], v_cache [pages, G, page, V]; slots null: nothing is cached.
+// `part` (float32 [splits, T, stride], 16-byte aligned) set: the projection is still the partial sums of a product
+// cut along K; the kernel sums them on the way, and of `proj` only the q columns are written.  bfloat16 rows of heads
+// that are multiples of 8 wide only (TS_ERR_ALIGN otherwise: the caller finishes the product first).
+TS_API int ts_rope_headnorm_write_supports_parts(int stride, int k_off, int D, int dtype) {
+  return dtype == TS_BF16 && D % 8 == 0 && stride % 8 == 0 && k_off % 8 == 0;
+}
+
 TS_API int ts_rope_headnorm_write(void* proj, int stride, int k_off, int v_off, const int* positions, const float* freq,
                                   int rot_dims, int norm, float eps, void* k_cache, void* v_cache, const int* slots, int T,
-                                  int H, int G, int D, int V, int page, int dtype, void* stream) {
+                                  int H, int G, int D, int V, int page, int dtype, const float* part, int splits,
+                                  void* stream) {
   if (T <= 0) return 0;
+  if (part != nullptr && (!ts_rope_headnorm_write_supports_parts(stride, k_off, D, dtype) || ((uintptr_t)part & 15) ||
+                          ((uintptr_t)proj & 15) || ((uintptr_t)k_cache & 15) || splits < 1))
+    TS_REFUSE(TS_ERR_ALIGN, "ts_rope_headnorm_write: unreduced input needs bfloat16 heads of multiples of 8 on 16-byte boundaries");
   if (rot_dims < 0 || rot_dims % 2 || rot_dims > D) TS_REFUSE(TS_ERR_SHAPE, "ts_rope_headnorm_write: %d rotated dimensions of %d", rot_dims, D);
   if (rot_dims > 0 && freq == nullptr) TS_REFUSE(TS_ERR_SHAPE, "ts_rope_headnorm_write: a rotation without frequencies");
   if (D <= 0 || D > 4096) TS_REFUSE(TS_ERR_LIMIT, "ts_rope_headnorm_write: heads of %d (limit 4096)", D);
@@ -376,6 +496,15 @@ TS_API int ts_rope_headnorm_write(void* proj, int stride, int k_off, int v_off, 
     cudaError_t e1 = cudaFuncSetAttribute(rope_headnorm_write_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaError_t e2 = cudaFuncSetAttribute(rope_headnorm_write_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e1 != cudaSuccess || e2 != cudaSuccess) TS_REFUSE((int)(e1 != cudaSuccess ? e1 : e2), "ts_rope_headnorm_write: shared memory %zu", smem);
+  }
+  if (dtype == TS_BF16 && D % 8 == 0 && stride % 8 == 0 && k_off % 8 == 0 && !((uintptr_t)proj & 15) && !((uintptr_t)k_cache & 15)) {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(rope_headnorm_write_vec_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) TS_REFUSE((int)e, "ts_rope_headnorm_write: shared memory %zu", smem);
+    }
+    ts_launch(rope_headnorm_write_vec_kernel, dim3(T, groups), dim3(RHN_WARPS * 32), smem, s, (bf16*)proj, stride, k_off, v_off,
+              positions, freq, rot_dims, norm, eps, (bf16*)k_cache, (bf16*)v_cache, slots, H, G, D, V, page, part, splits);
+    TS_LAUNCH_CHECK();
   }
   TS_BY_TYPE("ts_rope_headnorm_write",
              ts_launch(rope_headnorm_write_kernel<TT>, dim3(T, groups), dim3(RHN_WARPS * 32), smem, s, (TT*)proj, stride, k_off,

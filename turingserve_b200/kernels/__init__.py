@@ -68,7 +68,7 @@ class LazyProduct:
 class CudaOps:
     """ctypes front of ``libturingserve_b200.so``."""
 
-    ABI = 11
+    ABI = 12
     UNSUPPORTED = -4            # a kernel's refusal of a shape or layout another kernel takes
 
     def __init__(self, lib_path: str) -> None:
@@ -126,7 +126,8 @@ class CudaOps:
             "ts_head_gated_rmsnorm": [P, P, P, I, P, F, I, I, I, I, P],
             "ts_attention_biased": [P, I, I, P, I, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, P, I, I, P, P, I, I, P, P],
             "ts_attention_biased_mma": [P, I, I, P, I, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, P, I, I, P, P, I, I, P, P],
-            "ts_rope_headnorm_write": [P, I, I, I, P, P, I, I, F, P, P, P, I, I, I, I, I, I, I, P],
+            "ts_rope_headnorm_write": [P, I, I, I, P, P, I, I, F, P, P, P, I, I, I, I, I, I, I, P, I, P],
+            "ts_rope_headnorm_write_supports_parts": [I, I, I, I],
             "ts_rms_rows": [P, P, I, I, I, P, F, I, I, P],
             "ts_qk_rownorm_write": [P, I, P, P, F, P, F, I, P, P, P, I, I, I, I, I, I, P],
             "ts_latent_kv_write": [P, I, I, P, F, P, P, F, I, P, P, I, I, I, I, I, P],
@@ -730,15 +731,27 @@ class CudaOps:
                                              _code(src.dtype), self._stream()), "rotate_pairs")
 
     def rope_headnorm_write(self, proj, k_off: int, v_off: int, positions, freq, rot_dims: int, norm_eps, k_cache, v_cache,
-                            slots, H: int, G: int, D: int, V: int, page_size: int) -> None:
+                            slots, H: int, G: int, D: int, V: int, page_size: int):
         """``proj`` [T, ...]: q heads in the columns [0, H D), k heads from ``k_off``, value rows from ``v_off``.  Every q and
         k head has dimension i < rot_dims / 2 turned with dimension i + rot_dims / 2 by position * freq[i] (32-bit) and,
         with ``norm_eps`` not None, is then divided by its root mean square (eps inside the root, no weight); q in place,
-        k into ``k_cache`` and the value rows into ``v_cache`` at ``slots`` (None: nothing is cached)."""
+        k into ``k_cache`` and the value rows into ``v_cache`` at ``slots`` (None: nothing is cached).  ``proj`` may be a
+        product put off: the kernel then finishes its sum on the way (of the returned tensor only the q columns are
+        written).  Returns the projection tensor."""
+        proj = self._settle(proj)
+        part, splits = None, 0
+        if isinstance(proj, Deferred):
+            d = proj
+            if (d.bias is None and self.lib.ts_rope_headnorm_write_supports_parts(d.out.stride(0), k_off, D, _code(d.dtype))
+                    and all(t is None or t.data_ptr() % 16 == 0 for t in (d.out, d.part, k_cache))):
+                part, splits, proj = d.part, d.splits, d.out
+            else:
+                proj = self.materialize(d)
         self._check(self.lib.ts_rope_headnorm_write(
             _ptr(proj), proj.stride(0), k_off, v_off, _ptr(positions), _ptr(freq), int(rot_dims), 0 if norm_eps is None else 1,
             float(norm_eps or 0.0), _ptr(k_cache), _ptr(v_cache), _ptr(slots), proj.shape[0], H, G, D, V, page_size,
-            _code(proj.dtype), self._stream()), "rope_headnorm_write")
+            _code(proj.dtype), _ptr(part), splits, self._stream()), "rope_headnorm_write")
+        return proj
 
     # bfloat16 per-head products with at least this many rows go to the library's batched product
     batched_library_rows = int(os.environ.get("TURINGSERVE_B200_BATCHED_LIBRARY_ROWS", "17"))

@@ -17,7 +17,6 @@ from __future__ import annotations
 
 import torch
 
-from turingserve_b200 import kernels
 from turingserve_b200.config.model_config import (
     BranchJoinSpec, GatedMLPSpec, HalfRotarySpec, LayerRun, LayerSpec, ModelConfig, RoutedMLPSpec, SinkAttentionSpec,
     StreamLayerNormSpec)
@@ -175,7 +174,8 @@ def make_config(*, width: int, vocab: int, layers: list[dict], eps: float = 1e-6
 class VofinexModel(DecoderModel):
     """The decoder with what this family adds around the layers: the embedding rows enter the 32-bit stream times a
     constant (the multiplication happens in 32-bit, inside the first layer's norm kernel); every pass of the
-    repeated span is opened by its own row of 'loop.step'; the logits are multiplied by a constant."""
+    repeated span is opened by its own row of 'loop.step'; the logits are multiplied by a constant (folded into the final
+    norm's weight and bias when they are loaded)."""
 
     def __init__(self, cfg: ModelConfig, dtype: torch.dtype, device, max_positions: int) -> None:
         super().__init__(cfg, dtype, device, max_positions)
@@ -204,10 +204,13 @@ class VofinexModel(DecoderModel):
             return None
         return self.pass_vectors[run.opens_pass]
 
-    def finish_logits(self, logits: torch.Tensor) -> torch.Tensor:
+    def load(self, names, tensors) -> None:
+        super().load(names, tensors)
+        # the head has no bias, so the constant that multiplies the logits multiplies the final norm's output instead:
+        # its 32-bit weight and bias take it once, here, and no step spends a kernel on it
         if self.logit_scale != 1.0:
-            logits.mul_(self.logit_scale)
-        return logits
+            self.final_norm.weight = (self.final_norm.weight * self.logit_scale).contiguous()
+            self.final_norm.bias = (self.final_norm.bias * self.logit_scale).contiguous()
 
 
 register_architecture(Architecture(NAME, parse_config, tensor_names, to_config_json, build_model=VofinexModel))

@@ -71,9 +71,10 @@ class SinkAttention(Mixer):
         H, G, D, V = self.H, self.G, self.D, self.V
         grp = step.groups[cache.group]
         proj = torch.empty((T, self.q_dim + self.k_dim + self.v_dim), dtype=x.dtype, device=x.device)
-        ops.linear(proj, x, self.w_qkv)
+        # (a few tokens: the product's partial sums are summed by the kernel that rotates them)
+        proj = ops.linear(proj, x, self.w_qkv, may_defer=True, lazy=False)
         # q rotated and normed in place; rotated, normed keys and the values into the cache
-        ops.rope_headnorm_write(proj, self.q_dim, self.q_dim + self.k_dim, step.positions,
+        proj = ops.rope_headnorm_write(proj, self.q_dim, self.q_dim + self.k_dim, step.positions,
                                 self.position.freq if self.rot_dims else None, self.rot_dims, self.norm_eps,
                                 cache.k, cache.v, grp.slot_mapping if cache.writable else None, H, G, D, V,
                                 cache.page_size)
