@@ -95,10 +95,11 @@ class RoutedMLP(FeedForward):
             return out
         up_width = (2 if self.gated else 1) * self.inter
         a = torch.empty((T * top, up_width), dtype=x.dtype, device=x.device)
-        # the experts' input rows in sorted order, weighted and rounded once (the products then read plain rows)
-        xs = torch.empty((T * top, self.hidden), dtype=x.dtype, device=x.device)
-        ops.moe_gather(xs, x, order, weights if self.on_input else None, top)
+        scale = weights if self.on_input else None
         if T * top >= self.LIBRARY_ROWS and x.is_cuda and not torch.cuda.is_current_stream_capturing():
+            # the experts' input rows in sorted order, weighted and rounded once (the products then read plain rows)
+            xs = torch.empty((T * top, self.hidden), dtype=x.dtype, device=x.device)
+            ops.moe_gather(xs, x, order, scale, top)
             bounds = offsets[: self.E + 1].tolist()                      # the one read-back of this path
             for e in range(self.E):
                 lo, hi = bounds[e], bounds[e + 1]
@@ -110,11 +111,12 @@ class RoutedMLP(FeedForward):
                 if hi > lo:
                     ops.linear(y[lo:hi], a[lo:hi], self.w_down[e])
         elif self.gated:
-            ops.grouped_linear(a, xs, self.w_up, None, None, offsets, tiles, 1)
+            # (the first product fetches a pair's token row itself, weighted and rounded as the gather would)
+            ops.grouped_linear(a, x, self.w_up, order, scale, offsets, tiles, top)
             a = self._activate(a, T * top)
             ops.grouped_linear(y, a, self.w_down, None, None, offsets, tiles, 1)
         else:
-            ops.grouped_linear(a, xs, self.w_up, None, None, offsets, tiles, 1, self.activation)
+            ops.grouped_linear(a, x, self.w_up, order, scale, offsets, tiles, top, self.activation)
             ops.grouped_linear(y, a, self.w_down, None, None, offsets, tiles, 1)
         ops.moe_combine(out, y, place, None if self.on_input else weights, top, **passing)
         return out
