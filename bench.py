@@ -841,10 +841,11 @@ def pizunex_kernels(ops, z: dict, pk: dict, T: int, B: int, ctx: int, page: int)
 # layers of the same width and weight count ---------------------------------------------------------------------------
 VOFINEX_SIZES = {
     # width; heads, kv heads, head width (keys and values), rotated dimensions, block of positions; gated dense ff;
-    # experts with tensors, identity outputs, top, gated expert ff (three matrices: two thirds of Komirax's widths)
-    "1.5b": dict(width=1536, heads=12, kv_heads=2, dim=128, rot=64, size=1024, ff=8960, experts=8, identity=4, top=4, eff=1792,
+    # experts with tensors, identity outputs, top, gated expert ff (three matrices: two thirds of Komirax's widths).
+    # Blocks of 1,536 positions: a prompt of 2,048 tokens crosses one edge, and a token decoded at 2,048 sees 513 keys
+    "1.5b": dict(width=1536, heads=12, kv_heads=2, dim=128, rot=64, size=1536, ff=8960, experts=8, identity=4, top=4, eff=1792,
                  beside="1.5b"),
-    "7b": dict(width=3584, heads=28, kv_heads=4, dim=128, rot=64, size=1024, ff=18944, experts=8, identity=4, top=4, eff=4736,
+    "7b": dict(width=3584, heads=28, kv_heads=4, dim=128, rot=64, size=1536, ff=18944, experts=8, identity=4, top=4, eff=4736,
                beside="7b"),
 }
 
@@ -915,18 +916,21 @@ def vofinex_kernels(ops, z: dict, pk: dict, T: int, B: int, ctx: int, page: int)
         rows = reqs * per
         q = torch.randn(rows, H, D, device=dev).to(bf)
         o = torch.empty(rows, H, D, dtype=bf, device=dev)
-        step = SimpleNamespace(q_start=i32([i * per for i in range(reqs + 1)]), seq_lens=i32([seq] * reqs), num_requests=reqs,
-                               num_decode=reqs if per == 1 else 0, max_q_len=per, max_seq_len=seq)
         bt = torch.zeros(reqs, width, dtype=torch.int32, device=dev)
         n = -(-seq // page)
         for r in range(reqs):
             bt[r, :n] = torch.arange(1 + r * n, 1 + (r + 1) * n, dtype=torch.int32, device=dev)
         for tag, c in (("", size), ("_no_blocks", None)):
+            sq = seq
+            if c and per == 1:
+                sq = (seq - 1) // c * c                    # a single token at its block's last position: a full block of keys
+            step = SimpleNamespace(q_start=i32([i * per for i in range(reqs + 1)]), seq_lens=i32([sq] * reqs), num_requests=reqs,
+                                   num_decode=reqs if per == 1 else 0, max_q_len=per, max_seq_len=sq)
             ms = timed(lambda: ops.attention_biased(o, q, kc, vc, bt, step, G, page, D ** -0.5, 0.0, None, None, chunk=c,
                                                     sinks=sinks), flush)
-            seen = sum(i % c + 1 if c else i + 1 for i in range(seq - per, seq))       # keys a request's queries see
+            seen = sum(i % c + 1 if c else i + 1 for i in range(sq - per, sq))       # keys a request's queries see
             flops = 4.0 * D * H * seen * reqs
-            held = min(seq, (seq - 1) % c + 1 + (per - 1 if per > 1 else 0)) if c else seq
+            held = min(sq, (sq - 1) % c + 1 + (per - 1 if per > 1 else 0)) if c else sq
             byts = reqs * held * G * 2 * D * 2.0 + rows * H * D * 4.0
             out[f"sink_attention{tag}_{name}"] = {"us": round(ms * 1e3, 1), "tflops": round(flops / ms / 1e9, 1),
                                                   "frac_of_bf16": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 3),
