@@ -72,7 +72,7 @@ def test_stream_layer_norm_of_a_constant_row_is_the_bias_and_eps_sits_inside_the
 
 # -- rotation, per-head norm, cache write ------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,D,V,rot,page", [(4, 2, 16, 8, 8, 16), (3, 3, 24, 40, 24, 8), (6, 1, 128, 80, 32, 64),
+@pytest.mark.parametrize("H,G,D,V,rot,page", [(4, 2, 16, 8, 8, 16), (3, 3, 24, 40, 24, 8), (7, 1, 128, 72, 48, 64),
                                               (2, 1, 12, 20, 0, 4), (5, 5, 10, 6, 6, 16), (2, 2, 40, 24, 2, 8),
                                               (8, 2, 64, 64, 64, 32), (1, 1, 200, 3, 100, 16)])
 def test_rotation_by_halves_then_unit_heads_into_the_cache(ops, dtype, H, G, D, V, rot, page):
@@ -118,7 +118,7 @@ def test_rotation_by_halves_then_unit_heads_into_the_cache(ops, dtype, H, G, D, 
 
 
 @pytest.mark.parametrize("T", [1, 5, 8, 33, 100])
-@pytest.mark.parametrize("H,G,D,V,rot", [(6, 1, 128, 80, 32), (12, 2, 128, 128, 64), (4, 2, 64, 64, 64), (3, 3, 24, 40, 24)])
+@pytest.mark.parametrize("H,G,D,V,rot", [(6, 2, 128, 72, 32), (12, 2, 128, 128, 64), (4, 2, 64, 64, 64), (3, 3, 24, 40, 24)])
 def test_a_projection_left_unreduced_is_finished_by_the_rotation_kernel(ops, T, H, G, D, V, rot):
     """bfloat16, a few tokens: the q/k/v product leaves the partial sums of its cuts along K and the kernel that rotates
     sums them on the way: the same bits in q and in the cache as the finished product followed by the kernel."""
@@ -201,7 +201,7 @@ def plain_sink_attention(q, k, v, KVH, scale, size, sink, first_pos):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,KVH,Dk,Dv,page,size,sinks", [
-    (4, 2, 16, 8, 16, 9, True), (3, 3, 24, 40, 8, 33, True), (6, 1, 128, 80, 64, 50, True), (4, 1, 16, 16, 4, 20, False),
+    (4, 2, 16, 8, 16, 9, True), (3, 3, 24, 40, 8, 33, True), (6, 2, 128, 96, 64, 50, True), (4, 1, 16, 16, 4, 20, False),
     (6, 1, 8, 12, 8, None, True), (4, 2, 64, 64, 64, 64, True), (2, 1, 128, 128, 16, 100, True), (5, 5, 10, 6, 16, 7, True),
     (20, 1, 64, 64, 8, 40, True), (8, 2, 128, 128, 32, None, True), (40, 1, 128, 128, 16, 24, True)])
 def test_blocks_and_sinks_in_batches_of_unequal_requests(ops, dtype, H, KVH, Dk, Dv, page, size, sinks):
@@ -318,7 +318,7 @@ def test_the_sink_counts_once_unscaled_and_has_no_value(ops, dtype, D):
 
 # -- the router with a correction, gated experts, identity outputs -----------------------------------------------
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("outputs,top,K", [(5, 3, 72), (12, 4, 192), (4, 4, 48), (7, 1, 33), (2, 2, 32), (64, 6, 100)])
+@pytest.mark.parametrize("outputs,top,K", [(5, 3, 72), (11, 4, 160), (4, 4, 48), (7, 1, 33), (2, 2, 32), (64, 6, 100)])
 def test_the_correction_enters_the_choice_and_not_the_weights(ops, dtype, outputs, top, K):
     """Softmax over all router outputs; the choice by score + correction; the weights are the scores themselves, not
     renormalised.  A correction as large as the scores: the choice differs from the uncorrected one."""
@@ -384,7 +384,7 @@ def routed_part(dtype, W, ff, E, identity, top, g, monkeypatch=None):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("W,ff,E,identity,top,T", [(72, 24, 3, 2, 3, 50), (48, 20, 1, 3, 4, 33), (64, 16, 4, 0, 1, 90),
-                                                    (128, 64, 8, 4, 4, 1), (32, 12, 2, 2, 2, 7), (192, 64, 8, 4, 4, 400),
+                                                    (128, 64, 8, 4, 4, 1), (32, 12, 2, 2, 2, 7), (160, 48, 8, 3, 5, 400),
                                                     (40, 8, 0, 3, 2, 9)])
 def test_gated_experts_with_identity_outputs_against_the_plain_sum(ops, dtype, W, ff, E, identity, top, T, monkeypatch):
     """The routed feed-forward as a part, with the grouped kernels and with every expert's rows as a product of their

@@ -60,7 +60,7 @@ TINY = {
     "C": (dict(width=128, vocab=300, eps=1e-6, residual_mult=0.5, embedding_scale=11.3, logit_scale=1.5,
                loop={"start": 0, "stop": 2, "times": 1}, layers=[
         {**attn(4, 2, 64, 64, 0.19, size=64, rot=(500000.0, 32)), "mlp": dense(256)},
-        {**attn(4, 1, 128, 48, 0.13, size=100, rot=(500000.0, 64)), "mlp": moe(8, 4, 4, 64)},
+        {**attn(4, 1, 128, 48, 0.13, size=100, rot=(500000.0, 64)), "mlp": moe(7, 4, 5, 64)},
         {**attn(2, 1, 128, 128, 0.13, size=128, rot=(10000.0, 128)), "mlp": moe(8, 2, 2, 32)},
     ]), 33, 64),
     # the span is the whole model, twice; a single layer
