@@ -74,7 +74,8 @@ def test_stream_layer_norm_of_a_constant_row_is_the_bias_and_eps_sits_inside_the
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,D,V,rot,page", [(4, 2, 16, 8, 8, 16), (3, 3, 24, 40, 24, 8), (7, 1, 128, 72, 48, 64),
                                               (2, 1, 12, 20, 0, 4), (5, 5, 10, 6, 6, 16), (2, 2, 40, 24, 2, 8),
-                                              (8, 2, 64, 64, 64, 32), (1, 1, 200, 3, 100, 16)])
+                                              (8, 2, 64, 64, 64, 32), (1, 1, 200, 3, 100, 16), (2, 1, 256, 64, 128, 16),
+                                              (3, 1, 192, 40, 64, 8), (5, 2, 32, 16, 16, 8), (9, 3, 128, 128, 0, 16)])
 def test_rotation_by_halves_then_unit_heads_into_the_cache(ops, dtype, H, G, D, V, rot, page):
     """q in place; rotated, normed keys and untouched values at slots of a shuffled pool; positions far from 0 (the
     angle is computed in 32-bit from the position itself); rot = 0: no rotation; dims behind ``rot`` pass."""

@@ -300,9 +300,11 @@ rope_headnorm_write_kernel(T* __restrict__ proj, int stride, int k_off, int v_of
   }
 }
 
-// The same for bfloat16 rows whose heads are multiples of 8 wide and start on 16-byte boundaries: a lane brings 8
-// neighbouring columns with one 16-byte load, the rotation and the sum of squares run on the 32-bit copy in shared
-// memory (the same operations in the same order as above: the same bits), and 8 columns leave with one store.
+// The same for bfloat16 heads of up to 256 columns (a multiple of 8) on 16-byte boundaries whose rotated halves are
+// multiples of 8 too: a lane holds 8 neighbouring columns in registers (one 16-byte load, one 16-byte store), its
+// partner columns i +- R/2 come from the lane R/16 further by shuffles, and the block works the cosines and sines of
+// the token out once, into shared memory, for all its heads.  L lanes a head: 16 for heads of up to 128 columns (a
+// warp takes two heads), else 32.  The rotation's arithmetic is that of the kernel above, operation for operation.
 __device__ __forceinline__ void bf16x8_to_f(const uint4& v, float* f) {
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
@@ -313,6 +315,7 @@ __device__ __forceinline__ void bf16x8_to_f(const uint4& v, float* f) {
   }
 }
 
+template <int L>
 __global__ void __launch_bounds__(RHN_WARPS * 32)
 rope_headnorm_write_vec_kernel(bf16* __restrict__ proj, int stride, int k_off, int v_off, const int* __restrict__ positions,
                                const float* __restrict__ freq, int rot_dims, int norm, float eps, bf16* __restrict__ k_cache,
@@ -320,71 +323,78 @@ rope_headnorm_write_vec_kernel(bf16* __restrict__ proj, int stride, int k_off, i
                                const float* __restrict__ part, int splits) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float rhn_s[];
+  extern __shared__ __align__(16) float rhn_s[];                     // cosines [R/2], sines [R/2]
+  constexpr int PER = 32 / L;                                        // heads a warp
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int head = blockIdx.y * RHN_WARPS + warp;
+  const int sub = lane % L, which = lane / L;
+  const int head = (blockIdx.y * RHN_WARPS + warp) * PER + which;
+  const int c = sub * 8;                                             // this lane's first column of the head
+  const bool holds = head < H + G && c < D;
   const int slot = slots != nullptr ? slots[t] : -1;
   bf16* row = proj + (size_t)t * stride;
+  const int half = rot_dims / 2, hl = half / 8;
+  float* cs = rhn_s;
+  float* sn = rhn_s + half;
+  const float pos = (float)positions[t];
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * freq[i], sn + i, cs + i);
   // `part` set: the projection arrives unreduced, [splits, T, stride] partial sums; a column's value is their sum in
   // ascending order rounded to bfloat16, as the product's own last pass would have left it in `proj`
   const size_t split_stride = (size_t)gridDim.x * stride;
   const float* prow = part != nullptr ? part + (size_t)t * stride : nullptr;
-  if (head < H + G) {
-    float* x = rhn_s + warp * D;
-    const int col0 = head < H ? head * D : k_off + (head - H) * D;
-    bf16* src = row + col0;
+  const int col0 = !holds ? 0 : (head < H ? head * D : k_off + (head - H) * D);
+  bf16* src = row + col0 + (holds ? c : 0);
+  float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (holds) {
     if (prow == nullptr) {
-      for (int c = lane * 8; c < D; c += 256) bf16x8_to_f(*reinterpret_cast<const uint4*>(src + c), x + c);
+      bf16x8_to_f(*reinterpret_cast<const uint4*>(src), f);
     } else {
-      for (int c = lane * 8; c < D; c += 256) {
-        float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int sp = 0; sp < splits; ++sp) {
-          const float4* p4 = reinterpret_cast<const float4*>(prow + sp * split_stride + col0 + c);
-          const float4 a = p4[0], b = p4[1];
-          f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
-          f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
-        }
+      for (int sp = 0; sp < splits; ++sp) {
+        const float4* p4 = reinterpret_cast<const float4*>(prow + sp * split_stride + col0 + c);
+        const float4 a = p4[0], b = p4[1];
+        f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
+        f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
+      }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) x[c + j] = round_to<bf16>(f[j]);
-      }
+      for (int j = 0; j < 8; ++j) f[j] = round_to<bf16>(f[j]);
     }
-    __syncwarp();
-    const float pos = (float)positions[t];
-    const int half = rot_dims / 2;
-    float ss = 0.f;
-    for (int i = lane; i < half; i += 32) {
-      float sn, cs;
-      sincosf(pos * freq[i], &sn, &cs);
-      const float u = x[i], v = x[i + half];
-      const float a = u * cs - v * sn, b = v * cs + u * sn;
-      x[i] = a;
-      x[i + half] = b;
-      ss += a * a + b * b;
-    }
-    for (int i = rot_dims + lane; i < D; i += 32) {
-      const float v = x[i];
-      ss = fmaf(v, v, ss);
-    }
-    ss = warp_sum(ss);
-    __syncwarp();
-    const float r = norm ? 1.f / sqrtf(ss / (float)D + eps) : 1.f;
-    bf16* dst = src;
-    if (head >= H) {
-      dst = nullptr;
-      if (slot >= 0) {
-        const size_t pg = slot / page, off = slot % page;
-        dst = k_cache + ((pg * G + (head - H)) * page + off) * D;
-      }
-    }
-    if (dst != nullptr)
-      for (int c = lane * 8; c < D; c += 256) {
-        uint4 o;
-        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
+  }
+  __syncthreads();
+  // the lane that holds the other column of this lane's pairs (itself: columns that are not rotated)
+  const int partner = which * L + (sub < hl ? sub + hl : (sub < 2 * hl ? sub - hl : sub));
+  float g[8];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) h[j] = __halves2bfloat162(from_f<bf16>(x[c + 2 * j] * r), from_f<bf16>(x[c + 2 * j + 1] * r));
-        *reinterpret_cast<uint4*>(dst + c) = o;
-      }
+  for (int j = 0; j < 8; ++j) g[j] = __shfl_sync(0xffffffffu, f[j], partner);
+  if (sub < 2 * hl) {
+    const bool low = sub < hl;                                       // holds u of (u, v); else v
+    const int i0 = (low ? sub : sub - hl) * 8;
+    const float4 c0 = *reinterpret_cast<const float4*>(cs + i0), c1 = *reinterpret_cast<const float4*>(cs + i0 + 4);
+    const float4 s0 = *reinterpret_cast<const float4*>(sn + i0), s1 = *reinterpret_cast<const float4*>(sn + i0 + 4);
+    const float cv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = low ? f[j] * cv[j] - g[j] * sv[j] : f[j] * cv[j] + g[j] * sv[j];
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) ss = fmaf(f[j], f[j], ss);
+#pragma unroll
+  for (int o = L / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);        // (stays within the head's lanes)
+  const float r = norm ? 1.f / sqrtf(ss / (float)D + eps) : 1.f;
+  bf16* dst = src;
+  if (head >= H) {
+    dst = nullptr;
+    if (slot >= 0 && holds) {
+      const size_t pg = slot / page, off = slot % page;
+      dst = k_cache + ((pg * G + (head - H)) * page + off) * D + c;
+    }
+  }
+  if (holds && dst != nullptr) {
+    uint4 o;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = __halves2bfloat162(from_f<bf16>(f[2 * j] * r), from_f<bf16>(f[2 * j + 1] * r));
+    *reinterpret_cast<uint4*>(dst) = o;
   }
   if (blockIdx.y == 0 && slot >= 0 && v_cache != nullptr) {
     const size_t pg = slot / page, off = slot % page;
@@ -472,9 +482,10 @@ TS_API int ts_rotate_pairs(void* dst, int dst_ts, int dst_hs, const void* src, i
 // freq: 32-bit [rot_dims / 2].  k_cache [pages, G, page, D], v_cache [pages, G, page, V]; slots null: nothing is cached.
 // `part` (float32 [splits, T, stride], 16-byte aligned) set: the projection is still the partial sums of a product
 // cut along K; the kernel sums them on the way, and of `proj` only the q columns are written.  bfloat16 rows of heads
-// that are multiples of 8 wide only (TS_ERR_ALIGN otherwise: the caller finishes the product first).
+// that are multiples of 8 wide, at most 256, with a multiple of 16 rotated dimensions only (TS_ERR_ALIGN otherwise: the
+// caller finishes the product first).
 TS_API int ts_rope_headnorm_write_supports_parts(int stride, int k_off, int D, int dtype) {
-  return dtype == TS_BF16 && D % 8 == 0 && stride % 8 == 0 && k_off % 8 == 0;
+  return dtype == TS_BF16 && D % 8 == 0 && D <= 256 && stride % 8 == 0 && k_off % 8 == 0;
 }
 
 TS_API int ts_rope_headnorm_write(void* proj, int stride, int k_off, int v_off, const int* positions, const float* freq,
@@ -497,15 +508,17 @@ TS_API int ts_rope_headnorm_write(void* proj, int stride, int k_off, int v_off, 
     cudaError_t e2 = cudaFuncSetAttribute(rope_headnorm_write_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e1 != cudaSuccess || e2 != cudaSuccess) TS_REFUSE((int)(e1 != cudaSuccess ? e1 : e2), "ts_rope_headnorm_write: shared memory %zu", smem);
   }
-  if (dtype == TS_BF16 && D % 8 == 0 && stride % 8 == 0 && k_off % 8 == 0 && !((uintptr_t)proj & 15) && !((uintptr_t)k_cache & 15)) {
-    if (smem > 48 * 1024) {
-      cudaError_t e = cudaFuncSetAttribute(rope_headnorm_write_vec_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) TS_REFUSE((int)e, "ts_rope_headnorm_write: shared memory %zu", smem);
-    }
-    ts_launch(rope_headnorm_write_vec_kernel, dim3(T, groups), dim3(RHN_WARPS * 32), smem, s, (bf16*)proj, stride, k_off, v_off,
+  if (ts_rope_headnorm_write_supports_parts(stride, k_off, D, dtype) && rot_dims % 16 == 0 && !((uintptr_t)proj & 15) &&
+      !((uintptr_t)k_cache & 15)) {
+    const int per = D <= 128 ? 2 : 1;                                  // heads a warp
+    const int vgroups = ceil_div(H + G, RHN_WARPS * per);
+    const size_t vsmem = sizeof(float) * (rot_dims + 8);
+    auto kernel = per == 2 ? rope_headnorm_write_vec_kernel<16> : rope_headnorm_write_vec_kernel<32>;
+    ts_launch(kernel, dim3(T, vgroups), dim3(RHN_WARPS * 32), vsmem, s, (bf16*)proj, stride, k_off, v_off,
               positions, freq, rot_dims, norm, eps, (bf16*)k_cache, (bf16*)v_cache, slots, H, G, D, V, page, part, splits);
     TS_LAUNCH_CHECK();
   }
+  if (part != nullptr) TS_REFUSE(TS_ERR_ALIGN, "ts_rope_headnorm_write: unreduced input with %d rotated dimensions", rot_dims);
   TS_BY_TYPE("ts_rope_headnorm_write",
              ts_launch(rope_headnorm_write_kernel<TT>, dim3(T, groups), dim3(RHN_WARPS * 32), smem, s, (TT*)proj, stride, k_off,
                        v_off, positions, freq, rot_dims, norm, eps, (TT*)k_cache, (TT*)v_cache, slots, H, G, D, V, page));

@@ -742,7 +742,8 @@ class CudaOps:
         part, splits = None, 0
         if isinstance(proj, Deferred):
             d = proj
-            if (d.bias is None and self.lib.ts_rope_headnorm_write_supports_parts(d.out.stride(0), k_off, D, _code(d.dtype))
+            if (d.bias is None and int(rot_dims) % 16 == 0
+                    and self.lib.ts_rope_headnorm_write_supports_parts(d.out.stride(0), k_off, D, _code(d.dtype))
                     and all(t is None or t.data_ptr() % 16 == 0 for t in (d.out, d.part, k_cache))):
                 part, splits, proj = d.part, d.splits, d.out
             else:
