@@ -140,6 +140,8 @@ class TwinOps:
             y = 0.5 * z * (1.0 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z ** 3)))
         elif kind == "relu2":
             y = torch.relu(z) ** 2
+        elif kind == "gelu":
+            y = 0.5 * z * (1.0 + torch.erf(z * 0.7071067811865476))
         else:
             y = F.silu(z)
         out.copy_(y.to(out.dtype))
@@ -234,7 +236,7 @@ class TwinOps:
             rows = rows * row_scale.reshape(-1)[pairs][:, None]
         xs.copy_(rows.to(xs.dtype))
 
-    def moe_combine(self, out, y, place, pair_weights, top, x=None, pass_from=None):
+    def moe_combine(self, out, y, place, pair_weights, top, x=None, pass_from=None, add=None):
         rows = y[place.long()].view(out.shape[0], top, -1)
         if x is not None:
             own = (place.long() >= int(pass_from)).view(out.shape[0], top, 1)
@@ -244,6 +246,8 @@ class TwinOps:
         acc = torch.zeros(out.shape, dtype=torch.float32)
         for r in range(top):
             acc += rows[:, r]
+        if add is not None:
+            acc += add.float()
         out.copy_(acc.to(out.dtype))
 
 
@@ -471,6 +475,127 @@ def _attention_biased(self, out, q, k_cache, v_cache, block_tables, step, KVH, p
             p = torch.softmax(s, -1)[:, :seq_len]
             out[qs:qe, h] = (p @ vv[:, h // G]).to(out.dtype)
 
+
+# -- a residual stream in several copies, the state-space mixer, gates -----------------------------------------------
+def _hyper_norm(self, out, streams, y, mix, out_w, in_w, weight, eps, first=False, alpha=1.0):
+    T, S, h = streams.shape
+    y = self.materialize(y)
+    if first:
+        streams.copy_((alpha * y.float())[:, None, :].expand(T, S, h))
+    elif y is not None:
+        m = torch.eye(S) if mix is None else mix.float()
+        o = torch.ones(S) if out_w is None else out_w.float()
+        streams.copy_(torch.einsum("st,bsh->bth", m, streams) + o[None, :, None] * y.float()[:, None, :])
+    if out is None:
+        return
+    w_in = torch.ones(S) if in_w is None else in_w.float()
+    u = torch.einsum("s,bsh->bh", w_in, streams)
+    out.copy_((u / torch.sqrt(u.pow(2).mean(-1, keepdim=True) + eps) * weight.float()).to(out.dtype))
+
+
+def _ssm_prepare(self, ready, proj, xbc_off, dt_off, conv_w, conv_b, a_log, dt_bias, state, tail_off, step, H, channels, taps):
+    qs, slots = step.q_start.tolist(), step.state_slots.tolist()
+    for b in range(step.num_requests):
+        lo, hi = qs[b], qs[b + 1]
+        if hi <= lo:
+            continue
+        tail = state[slots[b]][tail_off:tail_off + (taps - 1) * channels].view(taps - 1, channels)
+        x = torch.cat([tail, proj[lo:hi, xbc_off:xbc_off + channels].float()], 0)
+        acc = conv_b.float().expand(hi - lo, channels).clone() if conv_b is not None else torch.zeros(hi - lo, channels)
+        for u in range(taps):
+            acc = acc + x[u:u + hi - lo] * conv_w.float()[:, u]
+        ready[lo:hi, :channels] = F.silu(acc)
+        dt = F.softplus(proj[lo:hi, dt_off:dt_off + H].float() + dt_bias.float())
+        ready[lo:hi, channels:channels + H] = dt
+        ready[lo:hi, channels + H:] = torch.exp(-torch.exp(a_log.float()) * dt)
+
+
+def _ssm_scan(self, out, ready, proj, xbc_off, state, skip, step, H, G, N, P, taps):
+    qs, slots = step.q_start.tolist(), step.state_slots.tolist()
+    inner, channels = H * P, H * P + 2 * G * N
+    for b in range(step.num_requests):
+        lo, hi = qs[b], qs[b + 1]
+        if hi <= lo:
+            continue
+        row = state[slots[b]]
+        S = row[:H * N * P].view(H, N, P)
+        for t in range(lo, hi):
+            x = ready[t, :inner].view(H, P)
+            Bm = ready[t, inner:inner + G * N].view(G, N).repeat_interleave(H // G, 0)
+            Cm = ready[t, inner + G * N:channels].view(G, N).repeat_interleave(H // G, 0)
+            dt, a = ready[t, channels:channels + H], ready[t, channels + H:]
+            S.mul_(a[:, None, None]).add_(dt[:, None, None] * Bm[:, :, None] * x[:, None, :])
+            y = torch.einsum("hnp,hn->hp", S, Cm)
+            if skip is not None:
+                y = y + skip.float()[:, None] * x
+            out[t] = y.reshape(-1)
+        if taps > 1:
+            tail = row[H * N * P:].view(taps - 1, channels)
+            tail.copy_(torch.cat([tail, proj[lo:hi, xbc_off:xbc_off + channels].float()], 0)[-(taps - 1):].clone())
+
+
+def _gate(g, kind):
+    return F.silu(g.float()) if kind == "silu" else torch.sigmoid(g.float())
+
+
+def _gated_group_rmsnorm(self, out, x, gate, weight, eps, groups=1, gate_kind="sigmoid", gate_first=False, scale=1.0):
+    T, n = x.shape
+    g = _gate(gate, gate_kind)
+    v = x.float() * g if gate_first else x.float()
+    v = v.view(T, groups, n // groups)
+    v = (v / torch.sqrt(v.pow(2).mean(-1, keepdim=True) + eps)).reshape(T, n) * weight.float()
+    if not gate_first:
+        v = v * g
+    out.copy_((v * scale).to(out.dtype))
+
+
+def _gate_mul(self, out, a, gate, gate_kind="sigmoid", scale=1.0):
+    out.copy_((a.float() * _gate(gate, gate_kind) * scale).to(out.dtype))
+
+
+def _act_mul(self, out, gu, act, group=0):
+    i = gu.shape[-1] // 2
+    if group:
+        blocks = gu.reshape(gu.shape[0], i // group, 2, group)
+        g, u = blocks[:, :, 0].reshape(-1, i), blocks[:, :, 1].reshape(-1, i)
+    else:
+        g, u = gu[..., :i], gu[..., i:]
+    a = torch.empty_like(g)
+    self.activation(a, g, act)
+    out.copy_((a.float() * u.float()).to(out.dtype))
+
+
+def _rope_pairs_write(self, proj, k_off, v_off, positions, freq, magnitude, rot_dims, k_cache, v_cache, slots, H, G, D, V,
+                      page_size):
+    T = proj.shape[0]
+
+    def turn(x):
+        if not rot_dims:
+            return x
+        a = positions.float()[:, None] * freq.float()[None, :rot_dims // 2]
+        c, s = (torch.cos(a) * magnitude)[:, None, :], (torch.sin(a) * magnitude)[:, None, :]
+        y = x.clone()
+        u, v = x[..., 0:rot_dims:2], x[..., 1:rot_dims:2]
+        y[..., 0:rot_dims:2] = u * c - v * s
+        y[..., 1:rot_dims:2] = v * c + u * s
+        return y
+
+    q = turn(proj[:, :H * D].float().reshape(T, H, D))
+    k = turn(proj[:, k_off:k_off + G * D].float().reshape(T, G, D)).to(proj.dtype)
+    proj[:, :H * D] = q.reshape(T, H * D).to(proj.dtype)
+    if slots is None:
+        return
+    v = proj[:, v_off:v_off + G * V].reshape(T, G, V)
+    for t, slot in enumerate(slots.tolist()):
+        if slot >= 0:
+            k_cache[slot // page_size, :, slot % page_size] = k[t]
+            v_cache[slot // page_size, :, slot % page_size] = v[t]
+
+
+for _name, _fn in (("hyper_norm", _hyper_norm), ("ssm_prepare", _ssm_prepare), ("ssm_scan", _ssm_scan),
+                   ("gated_group_rmsnorm", _gated_group_rmsnorm), ("gate_mul", _gate_mul), ("act_mul", _act_mul),
+                   ("rope_pairs_write", _rope_pairs_write)):
+    setattr(TwinOps, _name, _fn)
 
 for _name, _fn in (("delta_prepare", _delta_prepare), ("delta_scan", _delta_scan),
                    ("head_gated_rmsnorm", _head_gated_rmsnorm), ("rms_rows", _rms_rows),

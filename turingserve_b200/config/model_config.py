@@ -59,8 +59,8 @@ class AttentionSpec:
 
 @dataclass(frozen=True)
 class GatedMLPSpec:
-    """Dense gated feed-forward: down(act(gate(x)) * up(x)).  ``names``: the local tensor names of the gate, up
-    and down weights."""
+    """Dense gated feed-forward: down(act(gate(x)) * up(x)), act silu | gelu_tanh | gelu | relu2.  ``names``: the
+    local tensor names of the gate, up and down weights."""
 
     intermediate_size: int
     activation: str = "silu"
@@ -117,7 +117,9 @@ class SinkAttentionSpec:
     and k is divided by its root mean square (eps inside the root, no learned weight).  ``chunk`` c: position i
     sees j <= i only inside its own block of c positions, floor(i / c) = floor(j / c), blocks counted from the
     sequence's position 0.  ``window`` w: only i - w < j.  ``sinks``: the softmax's denominator also holds
-    exp(sink_h), a learned number per head without key or value, unscaled, counted once."""
+    exp(sink_h), a learned number per head without key or value, unscaled, counted once.  ``qkv_bias``: the q, k and v
+    projections have biases (tensor name + '.b').  ``out_gate``: the heads side by side are multiplied by
+    sigmoid(W_g h) ('g', a projection of the mixer's own input) before the output projection."""
 
     num_heads: int
     num_kv_heads: int
@@ -129,7 +131,84 @@ class SinkAttentionSpec:
     chunk: int | None = None
     window: int | None = None
     sinks: bool = True
+    qkv_bias: bool = False
+    out_gate: bool = False
     kind: str = "sink_attention"
+
+
+@dataclass(frozen=True)
+class HyperRMSNormSpec:
+    """RMS norm of what a sublayer reads from a residual stream kept as ``streams`` copies in 32-bit:
+    u = sum_s in[s] x_s, then u / sqrt(mean(u^2) + eps) * (weight_offset + weight), all in 32-bit, rounded once.
+    ``weight_offset`` 1: the weight is stored around zero.  The norm's kernel also carries out the write-back of the
+    sublayer before it (see ``StreamLinkSpec``)."""
+
+    eps: float
+    streams: int = 1
+    weight_offset: float = 0.0
+    weight_name: str = "weight"         # local tensor name of the scale ('' = the norm's prefix itself)
+    kind: str = "rmsnorm_hyper"
+
+
+@dataclass(frozen=True)
+class StreamLinkSpec:
+    """How one sublayer hangs on a residual stream of ``streams`` copies (hyper-connections): it reads
+    u = sum_s in[s] x_s and its output y comes back as x_t <- sum_s mix[s, t] x_s + out[t] y, all copies at once
+    from the old ones (mix indexed [from, to]).  ``learned`` False: no tensors, in = out = 1 and mix the identity,
+    which with one copy is the ordinary residual sum.  ``names``: local tensor names of in, out and mix."""
+
+    streams: int = 1
+    learned: bool = True
+    names: tuple[str, str, str] = ("in", "out", "mix")
+    kind: str = "stream_link"
+
+
+@dataclass(frozen=True)
+class BandScaledRotarySpec:
+    """Rotary position encoding over pairs of neighbouring dimensions (2i, 2i+1) of the first ``dims`` dimensions of
+    a head, angle = position * f_i, f_i = base^(-2i/dims), the frequencies rescaled by wavelength bands (the rule of
+    Llama 3.1): with l = 2 pi / f, f stays where l < original / high, becomes f / factor where l > original / low,
+    and between the two is (1 - s) f / factor + s f with s = (original / l - low) / (high - low).  ``factor`` None:
+    the plain frequencies."""
+
+    base: float
+    dims: int
+    factor: float | None = None
+    low: float = 1.0
+    high: float = 4.0
+    original: float = 8192.0
+    kind: str = "rope_pairs_banded"
+
+
+@dataclass(frozen=True)
+class PairedMixerSpec:
+    """Two mixers side by side that read the same input: ``left_scale`` * left(h) + ``right_scale`` * right(h).
+    ``names``: the prefixes of their tensors inside the mixer's own."""
+
+    left: Any
+    right: Any
+    left_scale: float = 1.0
+    right_scale: float = 1.0
+    names: tuple[str, str] = ("left.", "right.")
+    kind: str = "paired_mixer"
+
+
+@dataclass(frozen=True)
+class Mamba2Spec:
+    """Selective state-space mixer with a scalar decay per head.  One projection gives
+    [z (H P) | x (H P) | B (G N) | C (G N) | dt (H)]; x, B and C pass a causal filter of ``conv_taps`` taps per channel
+    (with bias) and SiLU; dt <- softplus(dt + dt_bias); per head (head h reads group h // (H / G)), with S [N, P]:
+    S <- exp(-exp(A_log_h) dt) S + dt B x^T,  y = S^T C + D_h x.  The heads side by side are multiplied by silu(z),
+    RMS-normed in ``norm_groups`` equal parts (each by its own root mean square) times a weight, and projected."""
+
+    num_heads: int
+    head_dim: int
+    state_size: int
+    num_groups: int
+    conv_taps: int
+    norm_groups: int
+    norm_eps: float
+    kind: str = "mamba2"
 
 
 @dataclass(frozen=True)
@@ -265,7 +344,8 @@ class RoutedMLPSpec:
     what the expert reads) or "output" (what it returns).  ``gated``: the experts are
     down(act(gate(.)) * up(.)).  ``correction``: a learned vector added to the scores for the choice only (the
     weights stay the scores).  ``identity``: so many more router outputs, behind the ``num_experts`` with
-    tensors, are experts that return their input."""
+    tensors, are experts that return their input.  ``shared_intermediate_size``: one more feed-forward of the same
+    form ('shared.up', 'shared.down') that every token uses, added unweighted."""
 
     num_experts: int
     top_k: int
@@ -277,6 +357,7 @@ class RoutedMLPSpec:
     gated: bool = False
     correction: bool = False
     identity: int = 0
+    shared_intermediate_size: int | None = None
     kind: str = "routed_mlp"
 
 

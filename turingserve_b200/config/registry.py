@@ -125,3 +125,5 @@ def _load_builtin() -> None:
         from turingserve_b200.models import pizunex  # noqa: F401
     if "Vofinex" not in _ARCHITECTURES:
         from turingserve_b200.models import vofinex  # noqa: F401
+    if "Gugezen" not in _ARCHITECTURES:
+        from turingserve_b200.models import gugezen  # noqa: F401

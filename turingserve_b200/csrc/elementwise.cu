@@ -5,6 +5,7 @@
 // model-dtype rounding points of its Triton kernels (turingserve/ops/triton_rmsnorm.py:10-27,
 // triton_silu_mul.py:10-18, triton_rope.py:10-24, triton_kv_write.py:10-25): statistics, the
 // rotation and the activation are computed in 32-bit and rounded once.
+#include "activations.cuh"
 #include "common.cuh"
 
 // ------------------------------------------------------------------------------------------
@@ -416,6 +417,70 @@ TS_API int ts_silu_mul_ex(void* out, const void* gu, int T, int inter, int group
     ts_launch(silu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (bf16*)out, (const bf16*)gu, inter, total, group);
   else
     TS_REFUSE(TS_ERR_DTYPE, "ts_silu_mul: dtype %d", dtype);
+  TS_LAUNCH_CHECK();
+}
+
+// The same with another gate activation: out[t, i] = T(act(g_i)) * u_i, act one of activations.cuh (32-bit arithmetic,
+// the activation rounded to the storage type, then the product rounded).
+template <typename T>
+__global__ void act_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int inter, size_t total, int group, int act) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int up_off = group ? group : inter;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / inter;
+    const int i = (int)(idx - t * inter);
+    const size_t gc = t * 2 * inter + gate_col(i, group);
+    out[idx] = from_f<T>(round_to<T>(ts_activate(to_f(gu[gc]), act)) * to_f(gu[gc + up_off]));
+  }
+}
+
+template <typename T>
+__global__ void act_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ gu, int inter, int vec_per_row,
+                                   unsigned total_vecs, int group, int act) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int N = Vec16<T>::N;
+  const int up_off = group ? group : inter;
+  for (unsigned v = blockIdx.x * blockDim.x + threadIdx.x; v < total_vecs; v += gridDim.x * blockDim.x) {
+    const unsigned t = v / vec_per_row;
+    const int i = (int)(v - t * vec_per_row) * N;
+    float g[N], u[N], o[N];
+    const size_t gc = (size_t)t * 2 * inter + gate_col(i, group);
+    load_vec<T, N>(gu + gc, g);
+    load_vec<T, N>(gu + gc + up_off, u);
+#pragma unroll
+    for (int k = 0; k < N; ++k) o[k] = round_to<T>(ts_activate(g[k], act)) * u[k];
+    store_vec<T, N>(out + (size_t)t * inter + i, o);
+  }
+}
+
+// act: a kind of activations.cuh (SiLU goes to ts_silu_mul_ex, whose bfloat16 instance uses the fast exponential).
+TS_API int ts_act_mul(void* out, const void* gu, int T, int inter, int group, int act, int dtype, void* stream) {
+  if (act == TS_ACT_SILU) return ts_silu_mul_ex(out, gu, T, inter, group, dtype, stream);
+  if (T <= 0) return 0;
+  if (act < 1 || act > TS_ACT_LAST) TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_act_mul: activation %d", act);
+  if (group < 0 || (group > 0 && (inter % group != 0 || group % 8 != 0)))
+    TS_REFUSE(TS_ERR_SHAPE, "ts_act_mul: blocks of %d columns for a width of %d", group, inter);
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t total = (size_t)T * inter;
+  const int n = dtype == TS_F32 ? 4 : 8;
+  const size_t vecs = total / n;
+  if ((dtype == TS_F32 || dtype == TS_BF16) && inter % n == 0 && vecs < 0xffffffffull && ((((uintptr_t)out | (uintptr_t)gu) & 15) == 0)) {
+    const int vb = (int)((vecs + 255) / 256 > 148 * 32 ? 148 * 32 : (vecs + 255) / 256);
+    if (dtype == TS_F32)
+      ts_launch(act_mul_vec_kernel<float>, dim3(vb), dim3(256), 0, s, (float*)out, (const float*)gu, inter, inter / n, (unsigned)vecs, group, act);
+    else
+      ts_launch(act_mul_vec_kernel<bf16>, dim3(vb), dim3(256), 0, s, (bf16*)out, (const bf16*)gu, inter, inter / n, (unsigned)vecs, group, act);
+    TS_LAUNCH_CHECK();
+  }
+  const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+  if (dtype == TS_F32)
+    ts_launch(act_mul_kernel<float>, dim3(blocks), dim3(256), 0, s, (float*)out, (const float*)gu, inter, total, group, act);
+  else if (dtype == TS_BF16)
+    ts_launch(act_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (bf16*)out, (const bf16*)gu, inter, total, group, act);
+  else
+    TS_REFUSE(TS_ERR_DTYPE, "ts_act_mul: dtype %d", dtype);
   TS_LAUNCH_CHECK();
 }
 

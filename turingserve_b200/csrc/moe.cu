@@ -119,7 +119,7 @@ router_topk_kernel(int* __restrict__ idx_out, float* __restrict__ w_out, const T
     __syncwarp();
   }
   if (renorm && lane == 0)
-    for (int r = 0; r < top; ++r) w_out[(size_t)t * top + r] /= total;
+    for (int r = 0; r < top; ++r) w_out[(size_t)t * top + r] /= (total + 1e-20f);
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -448,7 +448,7 @@ __global__ void moe_gather_kernel(T* __restrict__ xs, const T* __restrict__ x, c
 template <typename T>
 __global__ void moe_combine_kernel(T* __restrict__ out, const float* __restrict__ y, const int* __restrict__ place,
                                    const float* __restrict__ pair_w, int top, int N, const T* __restrict__ x,
-                                   const int* __restrict__ pass_from) {
+                                   const int* __restrict__ pass_from, const T* __restrict__ add) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -461,6 +461,7 @@ __global__ void moe_combine_kernel(T* __restrict__ out, const float* __restrict_
       const float v = at >= first_pass ? to_f(x[(size_t)t * N + n]) : y[(size_t)at * N + n];
       acc += pair_w != nullptr ? pair_w[p] * v : v;
     }
+    if (add != nullptr) acc += to_f(add[(size_t)t * N + n]);       // (an expert that every token uses)
     out[(size_t)t * N + n] = from_f<T>(acc);
   }
 }
@@ -566,15 +567,16 @@ TS_API int ts_grouped_linear(void* out, const void* x, const void* w, const int*
 }
 
 // x (out's type, [T, N]) and pass_from (one int on the device): pairs sorted to place *pass_from or later add the
-// token's own row of x instead of a row of y; both null: none do.
+// token's own row of x instead of a row of y; both null: none do.  add (out's type, [T, N], may be null): added to
+// every token's sum.
 TS_API int ts_moe_combine(void* out, const float* y, const int* place, const float* pair_w, int T, int top, int N, int dtype,
-                          const void* x, const int* pass_from, void* stream) {
+                          const void* x, const int* pass_from, const void* add, void* stream) {
   if (T <= 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == TS_F32)
-    ts_launch(moe_combine_kernel<float>, dim3(T), dim3(256), 0, s, (float*)out, y, place, pair_w, top, N, (const float*)x, pass_from);
+    ts_launch(moe_combine_kernel<float>, dim3(T), dim3(256), 0, s, (float*)out, y, place, pair_w, top, N, (const float*)x, pass_from, (const float*)add);
   else if (dtype == TS_BF16)
-    ts_launch(moe_combine_kernel<bf16>, dim3(T), dim3(256), 0, s, (bf16*)out, y, place, pair_w, top, N, (const bf16*)x, pass_from);
+    ts_launch(moe_combine_kernel<bf16>, dim3(T), dim3(256), 0, s, (bf16*)out, y, place, pair_w, top, N, (const bf16*)x, pass_from, (const bf16*)add);
   else
     TS_REFUSE(TS_ERR_DTYPE, "ts_moe_combine: dtype %d", dtype);
   TS_LAUNCH_CHECK();

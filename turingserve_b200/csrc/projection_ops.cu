@@ -525,6 +525,72 @@ TS_API int ts_rope_headnorm_write(void* proj, int stride, int k_off, int v_off, 
   TS_LAUNCH_CHECK();
 }
 
+// Rotation of NEIGHBOURING pairs (2i, 2i + 1), i < rot_dims / 2, of every q and k head by position * freq[i] (32-bit
+// product, sincosf), fused with the cache write: q heads in place, k heads into the key cache, the token's value rows
+// copied into the value cache.  One warp a (token, head); a lane takes whole pairs, so nothing crosses lanes.  The block
+// with blockIdx.y == 0 also copies the value rows.  A slot of -1 (or slots == null) caches nothing.
+template <typename T>
+__global__ void __launch_bounds__(RHN_WARPS * 32)
+rope_pairs_write_kernel(T* __restrict__ proj, int stride, int k_off, int v_off, const int* __restrict__ positions,
+                        const float* __restrict__ freq, float magnitude, int rot_dims, T* __restrict__ k_cache,
+                        T* __restrict__ v_cache, const int* __restrict__ slots, int H, int G, int D, int V, int page) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int head = blockIdx.y * RHN_WARPS + warp;
+  const int slot = slots != nullptr ? slots[t] : -1;
+  T* row = proj + (size_t)t * stride;
+  if (head < H + G) {
+    T* src = head < H ? row + (size_t)head * D : row + k_off + (size_t)(head - H) * D;
+    T* dst = src;
+    if (head >= H) {
+      dst = nullptr;
+      if (slot >= 0) {
+        const size_t pg = slot / page, off = slot % page;
+        dst = k_cache + ((pg * G + (head - H)) * page + off) * D;
+      }
+    }
+    if (dst != nullptr) {
+      const float pos = (float)positions[t];
+      for (int i = lane; i < rot_dims / 2; i += 32) {
+        float sn, cs;
+        sincosf(pos * freq[i], &sn, &cs);
+        sn *= magnitude;
+        cs *= magnitude;
+        const float u = to_f(src[2 * i]), v = to_f(src[2 * i + 1]);
+        dst[2 * i] = from_f<T>(u * cs - v * sn);
+        dst[2 * i + 1] = from_f<T>(v * cs + u * sn);
+      }
+      if (dst != src)
+        for (int i = rot_dims + lane; i < D; i += 32) dst[i] = src[i];
+    }
+  }
+  if (blockIdx.y == 0 && slot >= 0 && v_cache != nullptr) {
+    const size_t pg = slot / page, off = slot % page;
+    for (int i = threadIdx.x; i < G * V; i += blockDim.x) {
+      const int g = i / V, d = i % V;
+      v_cache[((pg * G + g) * page + off) * V + d] = row[v_off + i];
+    }
+  }
+}
+
+// proj [T, stride]: q heads in the columns [0, H D), k heads from k_off, value rows (G V) from v_off.
+TS_API int ts_rope_pairs_write(void* proj, int stride, int k_off, int v_off, const int* positions, const float* freq,
+                               float magnitude, int rot_dims, void* k_cache, void* v_cache, const int* slots, int T, int H,
+                               int G, int D, int V, int page, int dtype, void* stream) {
+  if (T <= 0) return 0;
+  if (rot_dims < 0 || rot_dims % 2 || rot_dims > D) TS_REFUSE(TS_ERR_SHAPE, "ts_rope_pairs_write: %d rotated dimensions of %d", rot_dims, D);
+  if (rot_dims > 0 && freq == nullptr) TS_REFUSE(TS_ERR_SHAPE, "ts_rope_pairs_write: a rotation without frequencies");
+  const int groups = ceil_div(H + G, RHN_WARPS);
+  if (groups > 65535) TS_REFUSE(TS_ERR_LIMIT, "ts_rope_pairs_write: %d heads", H + G);
+  cudaStream_t s = (cudaStream_t)stream;
+  TS_BY_TYPE("ts_rope_pairs_write",
+             ts_launch(rope_pairs_write_kernel<TT>, dim3(T, groups), dim3(RHN_WARPS * 32), 0, s, (TT*)proj, stride, k_off, v_off,
+                       positions, freq, magnitude, rot_dims, (TT*)k_cache, (TT*)v_cache, slots, H, G, D, V, page));
+  TS_LAUNCH_CHECK();
+}
+
 // out[t, h, :N] = w[h] (N x K) . x[t, h, :K]; w [H, N, K] contiguous; strides in elements.
 TS_API int ts_batched_linear(void* out, int out_ts, int out_hs, const void* x, int x_ts, int x_hs, const void* w, int T, int H,
                              int N, int K, int dtype, void* stream) {

@@ -176,6 +176,58 @@ __global__ void activation_parts_kernel(T* __restrict__ out, const float* __rest
   }
 }
 
+
+// gate functions of the kernels below
+enum TsGate : int { TS_GATE_SIGMOID = 0, TS_GATE_SILU = 1 };
+__device__ __forceinline__ float ts_gate(float g, int kind) {
+  const float sg = 1.f / (1.f + expf(-g));
+  return kind == TS_GATE_SILU ? g * sg : sg;
+}
+
+// An RMS norm over a 32-bit row in `groups` equal parts, each by its own root mean square, with a gate from a second
+// tensor that multiplies either what is normed (gate_first) or the normed result:
+//   gate_first:  v = x * gate(z);  out = T(v * rsqrt(mean_part(v^2) + eps) * w * scale)
+//   else:        out = T(x * rsqrt(mean_part(x^2) + eps) * w * gate(z) * scale)
+// grid (T, groups); out and the gate have row strides of their own (a column slice of a wider tensor).
+template <typename T>
+__global__ void gated_group_rmsnorm_kernel(T* __restrict__ out, int out_stride, const float* __restrict__ x,
+                                           const T* __restrict__ gate, int gate_stride, const float* __restrict__ w,
+                                           float eps, int n, int groups, int gate_kind, int gate_first, float scale) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[32];
+  const int m = n / groups, c0 = blockIdx.y * m;
+  const float* xr = x + (size_t)blockIdx.x * n + c0;
+  const T* gr = gate + (size_t)blockIdx.x * gate_stride + c0;
+  T* orow = out + (size_t)blockIdx.x * out_stride + c0;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < m; i += blockDim.x) {
+    float v = xr[i];
+    if (gate_first) v *= ts_gate(to_f(gr[i]), gate_kind);
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float rstd = 1.f / sqrtf(ss / (float)m + eps);
+  for (int i = threadIdx.x; i < m; i += blockDim.x) {
+    const float g = ts_gate(to_f(gr[i]), gate_kind);
+    const float v = gate_first ? xr[i] * g * rstd * w[c0 + i] : xr[i] * rstd * w[c0 + i] * g;
+    orow[i] = from_f<T>(v * scale);
+  }
+}
+
+// out[t, i] = T(a[t, i] * gate(z[t, i]) * scale): the gate on a mixer's heads before its output projection
+template <typename T>
+__global__ void gate_mul_kernel(T* __restrict__ out, int out_stride, const T* __restrict__ a, int a_stride,
+                                const T* __restrict__ gate, int gate_stride, int n, size_t total, int gate_kind, float scale) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / n;
+    const int i = (int)(idx - t * n);
+    out[t * out_stride + i] = from_f<T>(to_f(a[t * a_stride + i]) * ts_gate(to_f(gate[t * gate_stride + i]), gate_kind) * scale);
+  }
+}
+
 int threads_for(int n) { return n >= 2048 ? 512 : (n >= 512 ? 256 : 128); }
 
 }  // namespace
@@ -250,7 +302,7 @@ TS_API int ts_activation_parts(void* out, const float* part, int splits, const v
                                int dtype, void* stream) {
   const size_t n = (size_t)rows * cols;
   if (n == 0) return 0;
-  if (kind < 1 || kind > 3) TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_activation_parts: kind %d", kind);
+  if (kind < 1 || kind > TS_ACT_LAST) TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_activation_parts: kind %d", kind);
   cudaStream_t s = (cudaStream_t)stream;
   const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
   if (dtype == TS_F32)
@@ -264,10 +316,10 @@ TS_API int ts_activation_parts(void* out, const float* part, int splits, const v
   TS_LAUNCH_CHECK();
 }
 
-// kind: 1 tanh-form GELU, 2 squared ReLU, 3 SiLU.  out may be x.
+// kind: 1 tanh-form GELU, 2 squared ReLU, 3 SiLU, 4 GELU with the error function.  out may be x.
 TS_API int ts_activation(void* out, const void* x, long long n, int kind, int dtype, void* stream) {
   if (n <= 0) return 0;
-  if (kind < 1 || kind > 3) TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_activation: kind %d", kind);
+  if (kind < 1 || kind > TS_ACT_LAST) TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_activation: kind %d", kind);
   cudaStream_t s = (cudaStream_t)stream;
   const int blocks = (int)((n + 1023) / 1024 < 148 * 8 ? (n + 1023) / 1024 : 148 * 8);
   if (dtype == TS_F32)
@@ -276,5 +328,43 @@ TS_API int ts_activation(void* out, const void* x, long long n, int kind, int dt
     ts_launch(activation_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (bf16*)out, (const bf16*)x, (size_t)n, kind);
   else
     TS_REFUSE(TS_ERR_DTYPE, "ts_activation: dtype %d", dtype);
+  TS_LAUNCH_CHECK();
+}
+
+// x [T, n] 32-bit; gate [T, gate_stride] and out [T, out_stride] in `dtype`; w [n] 32-bit.  gate_kind: 0 sigmoid, 1 SiLU.
+TS_API int ts_gated_group_rmsnorm(void* out, int out_stride, const float* x, const void* gate, int gate_stride,
+                                  const float* w, float eps, int T, int n, int groups, int gate_kind, int gate_first,
+                                  float scale, int dtype, void* stream) {
+  if (T <= 0) return 0;
+  if (groups < 1 || n % groups) TS_REFUSE(TS_ERR_SHAPE, "ts_gated_group_rmsnorm: %d columns in %d parts", n, groups);
+  if (groups > 65535) TS_REFUSE(TS_ERR_LIMIT, "ts_gated_group_rmsnorm: %d parts", groups);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int th = threads_for(n / groups);
+  if (dtype == TS_F32)
+    ts_launch(gated_group_rmsnorm_kernel<float>, dim3(T, groups), dim3(th), 0, s, (float*)out, out_stride, x, (const float*)gate,
+              gate_stride, w, eps, n, groups, gate_kind, gate_first, scale);
+  else if (dtype == TS_BF16)
+    ts_launch(gated_group_rmsnorm_kernel<bf16>, dim3(T, groups), dim3(th), 0, s, (bf16*)out, out_stride, x, (const bf16*)gate,
+              gate_stride, w, eps, n, groups, gate_kind, gate_first, scale);
+  else
+    TS_REFUSE(TS_ERR_DTYPE, "ts_gated_group_rmsnorm: dtype %d", dtype);
+  TS_LAUNCH_CHECK();
+}
+
+// out [T, out_stride], a [T, a_stride], gate [T, gate_stride], n columns each.  out may be a.
+TS_API int ts_gate_mul(void* out, int out_stride, const void* a, int a_stride, const void* gate, int gate_stride, int T,
+                       int n, int gate_kind, float scale, int dtype, void* stream) {
+  const size_t total = (size_t)T * n;
+  if (total == 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+  if (dtype == TS_F32)
+    ts_launch(gate_mul_kernel<float>, dim3(blocks), dim3(256), 0, s, (float*)out, out_stride, (const float*)a, a_stride,
+              (const float*)gate, gate_stride, n, total, gate_kind, scale);
+  else if (dtype == TS_BF16)
+    ts_launch(gate_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (bf16*)out, out_stride, (const bf16*)a, a_stride,
+              (const bf16*)gate, gate_stride, n, total, gate_kind, scale);
+  else
+    TS_REFUSE(TS_ERR_DTYPE, "ts_gate_mul: dtype %d", dtype);
   TS_LAUNCH_CHECK();
 }

@@ -68,7 +68,7 @@ class LazyProduct:
 class CudaOps:
     """ctypes front of ``libturingserve_b200.so``."""
 
-    ABI = 12
+    ABI = 13
     UNSUPPORTED = -4            # a kernel's refusal of a shape or layout another kernel takes
 
     def __init__(self, lib_path: str) -> None:
@@ -119,7 +119,14 @@ class CudaOps:
             "ts_router_topk": [P, P, P, P, I, I, I, I, I, I, I, P, P],
             "ts_moe_align": [P, I, I, P, P, P, P, I, P],
             "ts_grouped_linear": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
-            "ts_moe_combine": [P, P, P, P, I, I, I, I, P, P, P],
+            "ts_moe_combine": [P, P, P, P, I, I, I, I, P, P, P, P],
+            "ts_hyper_norm": [P, P, P, P, I, P, P, P, P, P, F, I, I, I, I, F, I, P],
+            "ts_ssm_prepare": [P, P, I, I, I, P, P, P, P, P, ctypes.c_longlong, ctypes.c_longlong, P, P, P, I, I, I, I, I, P],
+            "ts_ssm_scan": [P, P, P, I, I, P, ctypes.c_longlong, P, P, P, I, I, I, I, I, I, I, P],
+            "ts_gated_group_rmsnorm": [P, I, P, P, I, P, F, I, I, I, I, I, F, I, P],
+            "ts_gate_mul": [P, I, P, I, P, I, I, I, I, F, I, P],
+            "ts_act_mul": [P, P, I, I, I, I, I, P],
+            "ts_rope_pairs_write": [P, I, I, I, P, P, F, I, P, P, P, I, I, I, I, I, I, I, P],
             "ts_moe_gather": [P, P, P, P, I, I, I, I, P],
             "ts_delta_prepare": [P, P, I, P, P, P, P, ctypes.c_longlong, P, P, P, I, I, I, I, I, I, F, I, P],
             "ts_delta_scan": [P, P, P, I, P, ctypes.c_longlong, P, P, I, I, I, I, I, I, I, I, P],
@@ -597,7 +604,7 @@ class CudaOps:
 
     diff_decode_splits = int(os.environ.get("TURINGSERVE_B200_DIFF_DECODE_SPLITS", "16"))
 
-    ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "relu2": 2, "silu": 3}
+    ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "relu2": 2, "silu": 3, "gelu": 4}
 
     def activation(self, out, x, kind: str) -> None:
         """out = act(x) elementwise (32-bit arithmetic, one rounding); out may be x.  ``x`` may be a product that
@@ -849,6 +856,90 @@ class CudaOps:
             Dk, Dv, page_size, float(scale), float(softcap), _ptr(slopes), w, splits, _ptr(scratch), _ptr(counters),
             _code(q.dtype), c, _ptr(sinks), self._stream()), "attention_biased")
 
+    # -- a residual stream in several copies -------------------------------------------------------------------
+    def hyper_norm(self, out, streams, y, mix, out_w, in_w, weight, eps: float, first: bool = False,
+                   alpha: float = 1.0) -> None:
+        """The norm of a residual stream kept as S copies (``streams`` float32 [T, S, h], updated in place).  First the
+        pending write-back of a sublayer's output ``y`` ([T, h]; a product put off is summed on the way; None: nothing
+        pending): x_t <- sum_s mix[s, t] x_s + out_w[t] y (``first``: every copy starts as alpha * y instead); then
+        u = sum_s in_w[s] x_s (``in_w`` None: the plain sum) and out = u / sqrt(mean(u^2) + eps) * weight (``out`` None:
+        only the write-back).  ``mix`` [S, S], ``out_w`` [S], ``in_w`` [S], ``weight`` [h]: float32 on the device;
+        ``mix`` / ``out_w`` None: identity / ones."""
+        T, S, h = streams.shape
+        part, splits, bias = None, 0, None
+        if isinstance(y, (LazyProduct, Deferred)):
+            y = self._settle(y)
+            if isinstance(y, Deferred):
+                part, splits, bias, dt = y.part, y.splits, y.bias, y.dtype
+                y = None
+        y = self.materialize(y)
+        if part is None:
+            dt = y.dtype if y is not None else out.dtype
+        self._check(self.lib.ts_hyper_norm(_ptr(out), _ptr(streams), _ptr(y), _ptr(part), splits, _ptr(bias), _ptr(mix),
+                                           _ptr(out_w), _ptr(in_w), _ptr(weight), float(eps), T, S, h, 1 if first else 0,
+                                           float(alpha), _code(dt), self._stream()), "hyper_norm")
+
+    # -- state-space mixer ---------------------------------------------------------------------------------------
+    def ssm_prepare(self, ready, proj, xbc_off: int, dt_off: int, conv_w, conv_b, a_log, dt_bias, state, tail_off: int,
+                    step, H: int, channels: int, taps: int) -> None:
+        """ready (float32 [T, channels + 2 H]) = [filtered channels | dt | a]: the ``channels`` columns of ``proj``
+        from ``xbc_off`` through their causal filters (``conv_w`` float32 [channels, taps], ``conv_b`` [channels]; the
+        inputs before the step's first token come from the request's state slot, from ``tail_off`` on) and SiLU;
+        dt = softplus(proj[dt_off + h] + dt_bias[h]), a = exp(-exp(a_log[h]) dt)."""
+        T = proj.shape[0]
+        self._check(self.lib.ts_ssm_prepare(_ptr(ready), _ptr(proj), proj.stride(0), xbc_off, dt_off, _ptr(conv_w),
+                                            _ptr(conv_b), _ptr(a_log), _ptr(dt_bias), _ptr(state), state.stride(0),
+                                            int(tail_off), _ptr(step.token_request), _ptr(step.q_start),
+                                            _ptr(step.state_slots), T, H, channels, taps, _code(proj.dtype),
+                                            self._stream()), "ssm_prepare")
+
+    def ssm_scan(self, out, ready, proj, xbc_off: int, state, skip, step, H: int, G: int, N: int, P: int, taps: int) -> None:
+        """out (float32 [T, H P]): per head S <- a S + dt B x^T, y = S^T C + skip_h x over the rows ``ssm_prepare`` made;
+        ``state`` (float32 [slots, H N P + (taps - 1) channels]) is read and left updated at each request's slot, the
+        filter's last inputs (from ``proj``) included."""
+        self._check(self.lib.ts_ssm_scan(_ptr(out), _ptr(ready), _ptr(proj), proj.stride(0), xbc_off, _ptr(state),
+                                         state.stride(0), _ptr(skip), _ptr(step.q_start), _ptr(step.state_slots),
+                                         step.num_requests, H, G, N, P, taps, _code(proj.dtype), self._stream()), "ssm_scan")
+
+    GATES = {"sigmoid": 0, "silu": 1}
+
+    def gated_group_rmsnorm(self, out, x, gate, weight, eps: float, groups: int = 1, gate_kind: str = "sigmoid",
+                            gate_first: bool = False, scale: float = 1.0) -> None:
+        """out [T, n] = RMS norm of ``x`` (float32 [T, n]) in ``groups`` equal parts, each by its own root mean square,
+        times ``weight`` (float32 [n]) and ``scale``; the gate (sigmoid or silu of ``gate``) multiplies what is normed
+        (``gate_first``) or the result.  ``out`` and ``gate`` may be column slices of wider tensors."""
+        T, n = x.shape
+        if gate.stride(1) != 1 or out.stride(1) != 1:
+            raise ValueError("gated_group_rmsnorm: rows must be contiguous")
+        self._check(self.lib.ts_gated_group_rmsnorm(_ptr(out), out.stride(0), _ptr(x), _ptr(gate), gate.stride(0),
+                                                    _ptr(weight), float(eps), T, n, int(groups), self.GATES[gate_kind],
+                                                    1 if gate_first else 0, float(scale), _code(out.dtype),
+                                                    self._stream()), "gated_group_rmsnorm")
+
+    def gate_mul(self, out, a, gate, gate_kind: str = "sigmoid", scale: float = 1.0) -> None:
+        """out = a * gate_fn(gate) * scale elementwise over [T, n] views with unit last stride (out may be a)."""
+        T, n = a.shape
+        if out.stride(1) != 1 or a.stride(1) != 1 or gate.stride(1) != 1:
+            raise ValueError("gate_mul: rows must be contiguous")
+        self._check(self.lib.ts_gate_mul(_ptr(out), out.stride(0), _ptr(a), a.stride(0), _ptr(gate), gate.stride(0), T, n,
+                                         self.GATES[gate_kind], float(scale), _code(a.dtype), self._stream()), "gate_mul")
+
+    def act_mul(self, out, gu, act: str, group: int = 0) -> None:
+        """out = act(gate) * up, the columns of ``gu`` laid out as ``silu_mul`` describes; ``act`` a one-input activation."""
+        T, inter = out.shape
+        self._check(self.lib.ts_act_mul(_ptr(out), _ptr(gu), T, inter, group, self.ACTIVATIONS[act], _code(gu.dtype),
+                                        self._stream()), "act_mul")
+
+    def rope_pairs_write(self, proj, k_off: int, v_off: int, positions, freq, magnitude: float, rot_dims: int, k_cache,
+                         v_cache, slots, H: int, G: int, D: int, V: int, page_size: int) -> None:
+        """``proj`` [T, ...]: q heads in the columns [0, H D), k heads from ``k_off``, value rows from ``v_off``.  Every q
+        and k head has its dimensions (2i, 2i + 1), i < rot_dims / 2, turned by position * freq[i] (32-bit); q in place,
+        k into ``k_cache`` and the value rows into ``v_cache`` at ``slots`` (None: nothing is cached)."""
+        self._check(self.lib.ts_rope_pairs_write(_ptr(proj), proj.stride(0), k_off, v_off, _ptr(positions), _ptr(freq),
+                                                 float(magnitude), int(rot_dims), _ptr(k_cache), _ptr(v_cache), _ptr(slots),
+                                                 proj.shape[0], H, G, D, V, page_size, _code(proj.dtype), self._stream()),
+                    "rope_pairs_write")
+
     # -- routed feed-forward ---------------------------------------------------------------------------------
     def router_topk(self, idx, weights, x, w_router, softmax: bool, renormalize: bool, correction=None) -> None:
         """idx (int32 [T, top]), weights (float32 [T, top]): the ``top`` experts with the largest router
@@ -891,13 +982,15 @@ class CudaOps:
         self._check(self.lib.ts_moe_gather(_ptr(xs), _ptr(x), _ptr(order), _ptr(row_scale), P, top, K, _code(x.dtype),
                                            self._stream()), "moe_gather")
 
-    def moe_combine(self, out, y, place, pair_weights, top: int, x=None, pass_from=None) -> None:
+    def moe_combine(self, out, y, place, pair_weights, top: int, x=None, pass_from=None, add=None) -> None:
         """out[t] = sum over a token's choices r of (pair_weights[t, r] *) y[place[t top + r]] (y float32).  With ``x``
         ([T, N], out's type) and ``pass_from`` (one int32 on the device): a pair sorted to that place or a later
-        one adds x[t] instead of a row of y (experts that return their input)."""
+        one adds x[t] instead of a row of y (experts that return their input).  ``add`` ([T, N], out's type): added
+        to every token's sum (the output of an expert that every token uses)."""
         T, N = out.shape
         self._check(self.lib.ts_moe_combine(_ptr(out), _ptr(y), _ptr(place), _ptr(pair_weights), T, top, N,
-                                            _code(out.dtype), _ptr(x), _ptr(pass_from), self._stream()), "moe_combine")
+                                            _code(out.dtype), _ptr(x), _ptr(pass_from), _ptr(add), self._stream()),
+                    "moe_combine")
 
     PAIR_PLAIN, PAIR_GATED = 0, 1
     # The many-row products whose epilogue saves a kernel (gate/up with the activation, q/k/v with rotation and

@@ -41,7 +41,7 @@ class ParamSpec:
     shape: tuple[int, ...]
     compute_dtype: bool = True
     integer: bool = False
-    init: str = "normal"            # "normal" | "ones" | "zeros": how the random-weights mode fills it
+    init: str = "normal"            # "normal" | "ones" | "zeros" | "identity": how the random-weights mode fills it
 
 
 @dataclass(frozen=True)
@@ -99,6 +99,21 @@ class Mixer(Part):
     def forward(self, x: torch.Tensor, step, cache, state: torch.Tensor | None) -> torch.Tensor:
         raise NotImplementedError
 
+    # A mixer of the form  W_out f(W_in x + b)  may expose its two products, so that a mixer made of several
+    # (``parts.paired_mixer``) runs ONE input product and ONE output product for all of them:
+    #   in_projection()  -> (weight [n_in, hidden], bias [n_in] or None), after load()
+    #   out_projection() -> weight [hidden, n_heads]
+    #   heads_forward(proj [T, n_in], step, cache, state, out [T, n_heads], scale): out = scale * f(proj); ``proj`` and
+    #   ``out`` are column slices of wider tensors (rows not contiguous).
+    def in_projection(self):
+        raise NotImplementedError(f"{type(self).__name__} does not expose its projections")
+
+    def out_projection(self):
+        raise NotImplementedError(f"{type(self).__name__} does not expose its projections")
+
+    def heads_forward(self, proj, step, cache, state, out, scale: float = 1.0) -> None:
+        raise NotImplementedError(f"{type(self).__name__} does not expose its projections")
+
 
 class FeedForward(Part):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -117,6 +132,16 @@ class BranchSum:
     scale: float = 1.0
 
 
+@dataclass
+class StreamUpdate:
+    """What a sublayer on a residual stream of several copies leaves pending: its output ``y`` (a tensor or a product
+    put off) and the link (``parts.stream_link.StreamLink``: the mix matrix and the output weights) by which it comes
+    back into the copies.  The norm that follows carries the write-back out in its own kernel."""
+
+    y: Any
+    link: Any
+
+
 @dataclass(frozen=True)
 class BuildContext:
     """What every part constructor gets besides its spec."""
@@ -128,13 +153,13 @@ class BuildContext:
 
 
 _REGISTRIES: dict[str, dict[str, Callable[[Any, BuildContext], Any]]] = {
-    "norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "block": {},
+    "norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "block": {}, "link": {},
 }
 
 
 def register(family: str, kind: str, factory: Callable[[Any, BuildContext], Any]) -> None:
     """Register ``factory(spec, ctx) -> part`` for ``spec.kind == kind`` in ``family``
-    (norm | position | mixer | feed_forward | block)."""
+    (norm | position | mixer | feed_forward | block | link)."""
     _REGISTRIES[family][kind] = factory
 
 
@@ -157,8 +182,8 @@ def _load_builtin() -> None:
     if not _loaded:
         _loaded = True
         from turingserve_b200.parts import (  # noqa: F401
-            attention, block, capped_attention, delta_rule, diff_attention, gated_mlp, latent_attention, lightning, mlp,
-            rmsnorm, rotary, routed_mlp, sink_attention)
+            attention, block, capped_attention, delta_rule, diff_attention, gated_mlp, latent_attention, lightning, mamba2,
+            mlp, paired_mixer, rmsnorm, rotary, routed_mlp, sink_attention, stream_link)
 
 
 def build_block(layer_spec: Any, ctx: BuildContext):

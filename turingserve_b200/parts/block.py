@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 
 from turingserve_b200 import kernels
-from turingserve_b200.parts.base import BranchSum, BuildContext, build, register
+from turingserve_b200.parts.base import BranchSum, BuildContext, StreamUpdate, build, register
 
 
 class PreNormBlock:
@@ -110,6 +110,48 @@ class ParallelBlock:
         return BranchSum(a, b, self.scale), residual
 
 
+class HyperBlock:
+    """Pre-norm wiring over a residual stream kept as several copies in 32-bit (hyper-connections): every sublayer
+    reads a weighted sum of the copies through its norm and its output comes back into all copies through its link
+    (``parts.stream_link``).  Each write-back is put off into the norm that follows, so the block carries (what is
+    pending, the copies [T, S, hidden]).  Roles: ``mixer_norm``, ``mixer``, ``mixer_link`` and, where the layer has a
+    feed-forward, ``ffn_norm``, ``feed_forward``, ``ffn_link``."""
+
+    def __init__(self, spec, ctx: BuildContext) -> None:
+        self.hidden = ctx.hidden_size
+        self.mixer_norm = build("norm", spec.mixer_norm, ctx)
+        self.mixer = build("mixer", spec.mixer, ctx)
+        self.mixer_link = build("link", spec.mixer_link, ctx)
+        self.S = self.mixer_link.S
+        self.has_ff = "feed_forward" in spec.roles
+        self.ffn_norm = build("norm", spec.ffn_norm, ctx) if self.has_ff else None
+        self.feed_forward = build("feed_forward", spec.feed_forward, ctx) if self.has_ff else None
+        self.ffn_link = build("link", spec.ffn_link, ctx) if self.has_ff else None
+        if self.has_ff and self.ffn_link.S != self.S:
+            raise ValueError("a layer's sublayers hang on the same number of stream copies")
+
+    def parts(self) -> dict[str, object]:
+        p = {"mixer_norm": self.mixer_norm, "mixer": self.mixer, "mixer_link": self.mixer_link}
+        if self.has_ff:
+            p.update(ffn_norm=self.ffn_norm, feed_forward=self.feed_forward, ffn_link=self.ffn_link)
+        return p
+
+    def forward(self, h, residual, step, cache, state, inject=None):
+        if inject is not None:
+            raise ValueError("hyper_streams: nothing is injected into the copies of the stream")
+        first = residual is None
+        if first:
+            rows = h.first if isinstance(h, BranchSum) else h
+            residual = torch.empty((rows.shape[0], self.S, self.hidden), dtype=torch.float32, device=rows.device)
+        x = self.mixer_norm.forward(h, residual, self.mixer_link, first=first)
+        pending = StreamUpdate(self.mixer.forward(x, step, cache, state), self.mixer_link)
+        if self.has_ff:
+            x = self.ffn_norm.forward(pending, residual, self.ffn_link)
+            pending = StreamUpdate(self.feed_forward.forward(x), self.ffn_link)
+        return pending, residual
+
+
 register("block", "pre_norm", _build_block)
+register("block", "hyper_streams", lambda spec, ctx: HyperBlock(spec, ctx))
 register("block", "parallel", lambda spec, ctx: ParallelBlock(spec, ctx))
 register("block", "pre_norm_stream", lambda spec, ctx: StreamBlock(spec, ctx))

@@ -1,5 +1,7 @@
-"""Dense gated feed-forward: down(silu(gate(x)) * up(x)), gate and up fused into one product
+"""Dense gated feed-forward: down(act(gate(x)) * up(x)), gate and up fused into one product
 (turingserve/model/qwen2.py:35-36, turingserve/model/loader.py:84, turingserve/ops/reference.py:26-28).
+act is SiLU (the activation may then sit in the product's epilogue) or another one-input activation the kernels
+have (the two GELUs, squared ReLU: product, then the activation kernel).
 """
 
 from __future__ import annotations
@@ -12,8 +14,9 @@ from turingserve_b200.parts.base import BuildContext, FeedForward, ParamSpec, re
 
 class GatedMLP(FeedForward):
     def __init__(self, spec, ctx: BuildContext) -> None:
-        if spec.activation != "silu":
+        if spec.activation not in ("silu", "gelu_tanh", "gelu", "relu2"):
             raise ValueError(f"gated_mlp: activation {spec.activation!r} has no kernel")
+        self.activation = spec.activation
         self.hidden = ctx.hidden_size
         self.inter = int(spec.intermediate_size)
         self.bias = bool(spec.bias)
@@ -62,7 +65,12 @@ class GatedMLP(FeedForward):
         ops = kernels.ops()
         T = x.shape[0]
         act = torch.empty((T, self.inter), dtype=x.dtype, device=x.device)
-        ops.gated_linear(act, x, self.w_gate_up, self.b_gate_up, self.group)
+        if self.activation == "silu":
+            ops.gated_linear(act, x, self.w_gate_up, self.b_gate_up, self.group)
+        else:
+            gu = torch.empty((T, 2 * self.inter), dtype=x.dtype, device=x.device)
+            ops.linear(gu, x, self.w_gate_up, self.b_gate_up)
+            ops.act_mul(act, gu, self.activation, self.group)
         out = torch.empty((T, self.hidden), dtype=x.dtype, device=x.device)
         return ops.linear(out, act, self.w_down, self.b_down, may_defer=True)
 

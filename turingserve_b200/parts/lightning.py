@@ -27,7 +27,7 @@ class Lightning(Mixer):
         self.decays = tuple(float(d) for d in spec.decays)
         self.eps = float(spec.norm_eps)
         self.device = ctx.device
-        self.w_in = self.w_o = self.norm_w = self.decay = None
+        self.w_in = self.w_o = self.norm_w = self.norm_w32 = self.decay = None
 
     def parameters(self) -> dict[str, ParamSpec]:
         hd, hv = self.H * self.D, self.H * self.V
@@ -40,10 +40,27 @@ class Lightning(Mixer):
         self.w_in = torch.cat([t["q"], t["k"], t["v"], t["g"]], dim=0).contiguous()
         self.w_o = t["o"].contiguous()
         self.norm_w = t["norm"].contiguous()
+        self.norm_w32 = self.norm_w.float().contiguous()
         self.decay = torch.tensor(self.decays, dtype=torch.float32, device=self.w_o.device)
 
     def state_need(self) -> StateNeed:
         return StateNeed((self.H, self.D, self.V), torch.float32)
+
+    # -- the two products apart (a mixer made of several runs them fused with its other halves') -------------------
+    def in_projection(self):
+        return self.w_in, None
+
+    def out_projection(self):
+        return self.w_o
+
+    def heads_forward(self, proj, step, cache, state, out, scale: float = 1.0) -> None:
+        """``proj`` [T, q | k | v | gate]: the scan, then the norm over all heads times sigmoid(gate) and ``scale`` into
+        ``out`` [T, H V].  Both may be column slices of wider tensors."""
+        ops = kernels.ops()
+        hd, hv = self.H * self.D, self.H * self.V
+        o = torch.empty((proj.shape[0], hv), dtype=torch.float32, device=proj.device)
+        ops.lightning(o, proj, state, self.decay, step, self.H, self.D, self.V)
+        ops.gated_group_rmsnorm(out, o, proj[:, 2 * hd + hv:], self.norm_w32, self.eps, 1, "sigmoid", False, scale)
 
     def forward(self, x: torch.Tensor, step, cache, state: torch.Tensor) -> torch.Tensor:
         ops = kernels.ops()

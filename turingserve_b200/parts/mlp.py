@@ -1,5 +1,5 @@
 """Dense feed-forward without a gate: down(act(up(x))), act one of the one-input activations the kernels
-have (the tanh form of GELU, squared ReLU, SiLU).  No biases.
+have (the tanh form of GELU, the GELU with the error function, squared ReLU, SiLU).  No biases.
 """
 
 from __future__ import annotations
@@ -9,7 +9,7 @@ import torch
 from turingserve_b200 import kernels
 from turingserve_b200.parts.base import BuildContext, FeedForward, ParamSpec, register
 
-ACTIVATIONS = ("gelu_tanh", "relu2", "silu")
+ACTIVATIONS = ("gelu_tanh", "relu2", "silu", "gelu")
 
 
 class MLP(FeedForward):

@@ -82,6 +82,11 @@ class DecoderModel:
                 h, residual = self.blocks[run.layer].forward(h, residual, step, cache_views[r], states[r], inject=inject)
             else:
                 h, residual = self.blocks[run.layer].forward(h, residual, step, cache_views[r], states[r])
+        return self.finish(h, residual)
+
+    def finish(self, h, residual) -> torch.Tensor:
+        """The model's last norm over what the last layer left (the pending branch output and the stream).  A model
+        class whose stream is not one tensor overrides this."""
         return self.final_norm.forward(h, residual)
 
     def injection(self, run, h0):

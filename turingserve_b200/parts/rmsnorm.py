@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 
 from turingserve_b200 import kernels
-from turingserve_b200.parts.base import BranchSum, BuildContext, Norm, ParamSpec, register
+from turingserve_b200.parts.base import BranchSum, BuildContext, Norm, ParamSpec, StreamUpdate, register
 
 
 class RMSNorm(Norm):
@@ -98,6 +98,49 @@ class StreamLayerNorm(Norm):
         return out
 
 
+class HyperRMSNorm(Norm):
+    """The norm a sublayer reads a residual stream of several 32-bit copies through.  ``forward(pending, streams,
+    link)``: first the write-back of what the sublayer before left pending (a ``StreamUpdate``; a ``BranchSum`` with
+    ``first``: the embedding rows times a constant start every copy), then u = sum_s in[s] x_s with the weights of
+    ``link`` (None: the plain sum of the copies, which is what a model's last norm reads), then
+    u / sqrt(mean(u^2) + eps) * (weight_offset + weight) in the engine's type (32-bit arithmetic, one rounding)."""
+
+    def __init__(self, spec, ctx: BuildContext) -> None:
+        self.eps = float(spec.eps)
+        self.size = ctx.hidden_size
+        self.dtype = ctx.dtype
+        self.S = int(spec.streams)
+        self.offset = float(spec.weight_offset)
+        self.weight_name = str(spec.weight_name)
+        self.weight: torch.Tensor | None = None
+
+    def parameters(self) -> dict[str, ParamSpec]:
+        return {self.weight_name: ParamSpec((self.size,), compute_dtype=False, init="zeros" if self.offset else "ones")}
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        # in 32-bit, the offset added once: the kernel multiplies by one vector
+        self.weight = (tensors[self.weight_name].float() + self.offset).contiguous()
+
+    def forward(self, pending, streams: torch.Tensor | None = None, link=None, first: bool = False) -> torch.Tensor:
+        if streams is None:
+            raise ValueError("the stream norm needs the 32-bit copies it reads")
+        T = streams.shape[0]
+        out = torch.empty((T, self.size), dtype=self.dtype, device=streams.device)
+        in_w = None if link is None else link.w_in
+        ops = kernels.ops()
+        if first:
+            rows, alpha = (pending.first, pending.scale) if isinstance(pending, BranchSum) else (pending, 1.0)
+            ops.hyper_norm(out, streams, rows, None, None, in_w, self.weight, self.eps, first=True, alpha=alpha)
+        elif isinstance(pending, StreamUpdate):
+            ops.hyper_norm(out, streams, pending.y, pending.link.mix, pending.link.w_out, in_w, self.weight, self.eps)
+        elif pending is None:
+            ops.hyper_norm(out, streams, None, None, None, in_w, self.weight, self.eps)
+        else:
+            raise TypeError(f"rmsnorm_hyper: what is pending must be a StreamUpdate, not {type(pending).__name__}")
+        return out
+
+
 register("norm", "rmsnorm", RMSNorm)
+register("norm", "rmsnorm_hyper", HyperRMSNorm)
 register("norm", "layernorm_stream", StreamLayerNorm)
 register("norm", "rmsnorm_stream", StreamRMSNorm)

@@ -69,6 +69,38 @@ class HalfRotaryEncoding:
         self.freq = f.to(torch.float32).to(ctx.device).contiguous()
 
 
+class BandScaledPairEncoding:
+    """Rotation of neighbouring pairs (2i, 2i+1) with frequencies rescaled by wavelength bands.  No table over
+    positions: the kernels take the angle as position * ``freq[i]`` in 32-bit.  ``freq`` is float32 [dims / 2] on the
+    device, worked out in double and rounded once."""
+
+    pairing = "neighbours"
+    magnitude = 1.0
+
+    def __init__(self, spec, ctx: BuildContext) -> None:
+        self.dims = int(spec.dims)
+        if self.dims % 2 or self.dims < 0:
+            raise ValueError("the rotated dimensions come in pairs")
+        base = float(spec.base)
+        freqs = []
+        for i in range(self.dims // 2):
+            f = base ** (-2.0 * i / self.dims)
+            if spec.factor:
+                factor, low, high, original = float(spec.factor), float(spec.low), float(spec.high), float(spec.original)
+                wavelength = 2.0 * math.pi / f
+                if wavelength > original / low:
+                    f = f / factor
+                elif wavelength >= original / high:
+                    s = (original / wavelength - low) / (high - low)
+                    f = (1.0 - s) * f / factor + s * f
+            freqs.append(f)
+        self.freq = torch.tensor(freqs, dtype=torch.float64).to(torch.float32).to(ctx.device).contiguous()
+
+
+HalfRotaryEncoding.pairing = "halves"
+PairRotaryEncoding.pairing = "neighbours"
+
 register("position", "rope", RotaryEncoding)
+register("position", "rope_pairs_banded", BandScaledPairEncoding)
 register("position", "rope_half", HalfRotaryEncoding)
 register("position", "yarn_pairs", PairRotaryEncoding)

@@ -4,6 +4,9 @@ A learned correction may enter the choice (score + correction) without entering 
 more outputs than there are experts with tensors: the outputs behind them are experts that return their input,
 which cost no product (their pairs are sorted behind the others and the sum takes the token's own row for them).
 
+A shared expert (``shared_intermediate_size``: one more feed-forward of the experts' form under 'shared.') runs for every
+token and is added, unweighted, in the kernel that sums a token's choices.
+
 Router logits and scores are 32-bit.  The (token, choice) pairs are sorted by expert on the device and the
 two products run over the sorted groups; the chosen score multiplies the expert's input (``weight_on``
 "input", the product reads score * x rounded to the engine's type) or its output; a token's choices are
@@ -51,7 +54,9 @@ class RoutedMLP(FeedForward):
         self.outputs = self.E + self.identity           # what the router scores
         if self.top > self.outputs:
             raise ValueError(f"routed_mlp: top {self.top} of {self.outputs} router outputs")
-        self.w_router = self.w_up = self.w_down = self.correction = None
+        shared = getattr(spec, "shared_intermediate_size", None)
+        self.shared_inter = int(shared) if shared else 0
+        self.w_router = self.w_up = self.w_down = self.correction = self.w_shared_up = self.w_shared_down = None
 
     def parameters(self) -> dict[str, ParamSpec]:
         p = {"router": ParamSpec((self.outputs, self.hidden), compute_dtype=False)}
@@ -62,12 +67,20 @@ class RoutedMLP(FeedForward):
                 p[f"e{e}.gate"] = ParamSpec((self.inter, self.hidden))
             p[f"e{e}.up"] = ParamSpec((self.inter, self.hidden))
             p[f"e{e}.down"] = ParamSpec((self.hidden, self.inter))
+        if self.shared_inter:
+            if self.gated:
+                p["shared.gate"] = ParamSpec((self.shared_inter, self.hidden))
+            p["shared.up"] = ParamSpec((self.shared_inter, self.hidden))
+            p["shared.down"] = ParamSpec((self.hidden, self.shared_inter))
         return p
 
     def load(self, t: dict[str, torch.Tensor]) -> None:
         self.w_router = t["router"].float().contiguous()
         if self.has_correction:
             self.correction = t["correction"].float().contiguous()
+        if self.shared_inter:
+            self.w_shared_up = (torch.cat([t["shared.gate"], t["shared.up"]], dim=0) if self.gated else t["shared.up"]).contiguous()
+            self.w_shared_down = t["shared.down"].contiguous()
         if self.E == 0:
             return
         # gated experts: an expert's gate rows, then its up rows, in one product
@@ -89,6 +102,8 @@ class RoutedMLP(FeedForward):
         else:
             offsets, order, place, tiles = ops.moe_align(idx, self.E)
             passing = {}
+        if self.shared_inter:
+            passing["add"] = self._shared(x)
         y = torch.empty((T * top, self.hidden), dtype=torch.float32, device=x.device)
         if self.E == 0:
             ops.moe_combine(out, y, place, weights, top, **passing)
@@ -120,6 +135,20 @@ class RoutedMLP(FeedForward):
             ops.grouped_linear(y, a, self.w_down, None, None, offsets, tiles, 1)
         ops.moe_combine(out, y, place, None if self.on_input else weights, top, **passing)
         return out
+
+    def _shared(self, x: torch.Tensor) -> torch.Tensor:
+        """The expert that every token uses: down(act(up(x))), or the gated form."""
+        ops = kernels.ops()
+        T = x.shape[0]
+        a = torch.empty((T, self.shared_inter), dtype=x.dtype, device=x.device)
+        if self.gated:
+            gu = torch.empty((T, 2 * self.shared_inter), dtype=x.dtype, device=x.device)
+            ops.linear(gu, x, self.w_shared_up)
+            ops.silu_mul(a, gu, 0)
+        else:
+            ops.activation(a, ops.linear(a, x, self.w_shared_up, may_defer=True), self.activation)
+        out = torch.empty((T, self.hidden), dtype=x.dtype, device=x.device)
+        return ops.linear(out, a, self.w_shared_down)
 
     def _activate(self, a: torch.Tensor, rows: int) -> torch.Tensor:
         """The first ``rows`` rows of the experts' first product through the activation (the rows behind them belong

@@ -38,6 +38,8 @@ def random_tensors(cfg: ModelConfig, seed: int, std: float = 0.02,
             out[name] = torch.ones(spec.shape, dtype=dtype)
         elif spec.init == "zeros":
             out[name] = torch.zeros(spec.shape, dtype=dtype)
+        elif spec.init == "identity":
+            out[name] = torch.eye(*spec.shape, dtype=dtype)
         else:
             out[name] = (torch.randn(spec.shape, generator=g, dtype=torch.float32) * std).to(dtype)
     return out
@@ -73,6 +75,8 @@ def random_model_on_device(cfg: ModelConfig, dtype: torch.dtype, device, seed: i
             tensors[name] = torch.ones(spec.shape, dtype=kind, device=device)
         elif spec.init == "zeros":
             tensors[name] = torch.zeros(spec.shape, dtype=kind, device=device)
+        elif spec.init == "identity":
+            tensors[name] = torch.eye(*spec.shape, dtype=kind, device=device)
         else:
             t = torch.empty(spec.shape, dtype=kind, device=device)
             t.normal_(0.0, std, generator=g)
