@@ -6,9 +6,19 @@ the configuration as config.json spells it and the tensors by their checkpoint n
 
 from __future__ import annotations
 
+import json
 import math
+import os
 
 import torch
+from safetensors.torch import load_file
+
+
+def read_folder(folder: str, dtype=torch.float64):
+    with open(os.path.join(folder, "config.json"), encoding="utf-8") as f:
+        cfg = json.load(f)
+    tensors = load_file(os.path.join(folder, "model.safetensors"))
+    return cfg, {k: (v.to(dtype) if v.dtype.is_floating_point else v) for k, v in tensors.items()}
 
 
 # -- norms and activations -------------------------------------------------------------------------------------------

@@ -409,8 +409,8 @@ def _batched_linear(self, out, x, w):
 def _rope_headnorm_write(self, proj, k_off, v_off, positions, freq, rot_dims, norm_eps, k_cache, v_cache, slots, H, G, D, V,
                          page_size):
     T = proj.shape[0]
-    q = proj[:, :H * D].float().view(T, H, D)
-    k = proj[:, k_off:k_off + G * D].float().view(T, G, D)
+    q = proj[:, :H * D].float().reshape(T, H, D).clone()
+    k = proj[:, k_off:k_off + G * D].float().reshape(T, G, D).clone()
 
     def turn(x):
         if rot_dims:
@@ -571,7 +571,7 @@ def _rope_pairs_write(self, proj, k_off, v_off, positions, freq, magnitude, rot_
 
     def turn(x):
         if not rot_dims:
-            return x
+            return x.clone()
         a = positions.float()[:, None] * freq.float()[None, :rot_dims // 2]
         c, s = (torch.cos(a) * magnitude)[:, None, :], (torch.sin(a) * magnitude)[:, None, :]
         y = x.clone()

@@ -98,9 +98,11 @@ class SinkAttention(Mixer):
         grp = step.groups[cache.group]
         slots = grp.slot_mapping if cache.writable else None
         k_off, v_off = self.q_dim, self.q_dim + self.k_dim
-        if self.neighbours:
-            ops.rope_pairs_write(proj, k_off, v_off, step.positions, self.position.freq, float(self.position.magnitude),
-                                 self.rot_dims, cache.k, cache.v, slots, H, G, D, V, cache.page_size)
+        if self.neighbours or (not self.rot_dims and self.norm_eps is None):
+            # (without a rotation the same kernel is the plain cache write)
+            ops.rope_pairs_write(proj, k_off, v_off, step.positions, self.position.freq if self.rot_dims else None,
+                                 float(getattr(self.position, "magnitude", 1.0)), self.rot_dims, cache.k, cache.v, slots,
+                                 H, G, D, V, cache.page_size)
         else:
             ops.rope_headnorm_write(proj, k_off, v_off, step.positions, self.position.freq if self.rot_dims else None,
                                     self.rot_dims, self.norm_eps, cache.k, cache.v, slots, H, G, D, V, cache.page_size)
