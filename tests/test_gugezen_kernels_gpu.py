@@ -163,9 +163,9 @@ def test_neighbouring_pairs_turn_and_keys_and_values_reach_their_slots(ops, dtyp
     pos = positions.cpu()
     q_want = plain.rotate_neighbours(before[:, :H * D].double().cpu().view(T, H, D), pos, f)
     k_want = plain.rotate_neighbours(before[:, H * D:(H + G) * D].double().cpu().view(T, G, D), pos, f)
-    # angles up to 70,001 radians in 32-bit: an absolute error of a few 1e-3 there, nothing below position 1,000
+    # angles up to 70,001 radians in 32-bit: an absolute error of a few 1e-3 there, 3e-5 at position 500, nothing below 100
     loose = dict(rtol=2e-2, atol=3e-2) if dtype == torch.bfloat16 else dict(rtol=1e-4, atol=2e-2)
-    tight = tol(dtype)
+    tight = tol(dtype) if dtype == torch.bfloat16 else dict(rtol=1e-4, atol=1e-4)      # (32-bit frequencies times 60)
     got_q = proj[:, :H * D].double().cpu().view(T, H, D)
     far = pos > 1000
     assert torch.allclose(got_q[~far], q_want[~far], **{k_: float(v_) for k_, v_ in tight.items()})
@@ -353,7 +353,7 @@ def test_state_space_memory_kept_and_forgotten_and_long_decoding(ops):
     dt = math.log(2.0)
     keep = math.exp(-math.exp(-12.0) * dt) ** (T - 1 - 3)
     assert abs(float(out[-1, 0]) - dt * s5 * s5 * s5 * keep) < 1e-3 * s5 ** 3
-    assert abs(float(out[-1, P])) < 1e-20                      # the fast head forgot
+    assert abs(float(out[-1, P])) < 1e-10                      # the fast head forgot (silu(-20) is -4e-8, not 0)
     g = torch.Generator(device=DEV).manual_seed(5)
     H, P, N, G, taps = 3, 12, 20, 3, 3
     inner, channels, n_in = ssm_sizes(H, P, N, G)
@@ -397,9 +397,9 @@ def test_routed_experts_renormalised_with_a_shared_expert(ops, dtype, W, ff, E, 
         assert torch.allclose(got, want, rtol=1e-4, atol=1e-4)
     else:
         s = torch.softmax(x.double().cpu() @ Wd["p.router"].T, -1).sort(-1, descending=True).values
-        clear = (s[:, top - 1] - s[:, top] > 0.02) if top < E else torch.ones(T, dtype=torch.bool)
-        assert int(clear.sum()) >= T // 3
-        assert torch.allclose(got[clear], want[clear], rtol=4e-2, atol=4e-2)
+        clear = (s[:, top - 1] - s[:, top] > 0.15 * s[:, top - 1]) if top < E else torch.ones(T, dtype=torch.bool)
+        assert int(clear.sum()) >= T // 5
+        assert float((got[clear] - want[clear]).abs().max()) <= 2e-2 * float(want.abs().max())
 
 
 def test_router_weights_sum_to_one_and_the_largest_scores_win(ops):
@@ -425,4 +425,5 @@ def test_dense_feed_forward_with_a_gelu_gate(ops, dtype, W, ff, T):
     x = torch.randn(T, W, generator=g, device=DEV).to(dtype)
     got = ops.materialize(part.forward(x)).float().cpu()
     want = plain.dense_ff(x.double().cpu(), {"p." + k: v.double().cpu() for k, v in tensors.items()}, "p.").float()
-    assert torch.allclose(got, want, **({"rtol": 1e-4, "atol": 1e-4} if dtype == torch.float32 else {"rtol": 4e-2, "atol": 4e-2}))
+    # (sums over hundreds of rounded terms: the bound goes by the largest output)
+    assert float((got - want).abs().max()) <= (1e-5 if dtype == torch.float32 else 1.5e-2) * float(want.abs().max())
