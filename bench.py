@@ -974,6 +974,167 @@ def vofinex_kernels(ops, z: dict, pk: dict, T: int, B: int, ctx: int, page: int)
     return out
 
 
+# ---- Gugezen (a stream in several copies, attention with a sink and an output gate beside linear attention, the
+# state-space mixer, gated GELU and routed feed-forwards with a shared expert) beside Komirax layers ----------------
+GUGEZEN_SIZES = {
+    # width; attention half: heads, kv heads, head width, rotated dimensions; linear half: heads (key and value width as the
+    # attention's); state-space mixer: heads, head width, state rows, groups, taps, norm parts; gated dense ff (three
+    # matrices: two thirds of the Komirax width for the same weight count); experts, top, expert ff, shared expert ff
+    "1.5b": dict(width=1536, heads=12, kv_heads=2, dim=128, rot=128, lheads=6, sheads=48, sdim=64, state=128, sgroups=2, taps=4,
+                 parts=2, ff=8960, experts=8, top=2, eff=2688, shared=1344, streams=2, beside="1.5b"),
+    "7b": dict(width=3584, heads=28, kv_heads=4, dim=128, rot=128, lheads=14, sheads=112, sdim=64, state=128, sgroups=2, taps=4,
+               parts=2, ff=18944, experts=8, top=2, eff=7104, shared=3552, streams=2, beside="7b"),
+}
+
+
+def gugezen_config(z: dict, groups: int, vocab: int):
+    """``groups`` times four layers: (state-space, dense), (attention + linear attention, routed), (state-space, routed),
+    (attention + linear attention, dense)."""
+    from turingserve_b200.models.gugezen import make_config
+    pair = {"type": "parallel", "mixer": {
+        "left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+                 "rot": {"base": 500000.0, "dims": z["rot"], "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}},
+        "right": {"heads": z["lheads"], "dim": z["dim"], "vdim": z["dim"],
+                  "decay": [1.0 - 2.0 ** -(2 + 6 * i / max(1, z["lheads"] - 1)) for i in range(z["lheads"])]},
+        "left_scale": 0.8, "right_scale": 0.9}}
+    ssm = {"type": "mamba2", "mixer": {"heads": z["sheads"], "vdim": z["sdim"], "state": z["state"], "groups": z["sgroups"],
+                                       "conv": z["taps"], "norm_groups": z["parts"]}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["eff"]}, "router": {"experts": z["experts"], "top": z["top"]},
+           "shared": {"ff": z["shared"]}}
+    four = [{**ssm, "mlp": dense}, {**pair, "mlp": moe}, {**ssm, "mlp": moe}, {**pair, "mlp": dense}]
+    return make_config(width=z["width"], vocab=vocab, layers=four * groups, eps=1e-6, streams=z["streams"], embedding_scale=4.0,
+                       logit_scale=0.5)
+
+
+def gugezen_kernels(ops, z: dict, pk: dict, T: int, B: int, ctx: int, page: int) -> dict:
+    """Each kernel of the new mechanisms alone, beside the like kernel of the closest design: a portion of T tokens and B
+    single tokens at context ``ctx``."""
+    import torch
+    from types import SimpleNamespace
+    dev = torch.device("cuda", 0)
+    big = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    flush = lambda: big.fill_(1)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    out = {}
+    hbm = pk["hbm_gbs"] * 1e9
+    FP32_PEAK = 148 * 128 * 2 * 1.965e9                      # FFMA lanes x 2 x the highest SM clock: nominal
+    bf = torch.bfloat16
+    W, S = z["width"], z["streams"]
+    H, G, D, rot = z["heads"], z["kv_heads"], z["dim"], z["rot"]
+    frac = lambda byts, ms: round(byts / (ms / 1e3) / hbm, 3)
+
+    # the norm over the stream's copies (write-back of the pending output, read, norm) beside the one-copy stream norm
+    for name, rows in (("prefill", T), ("decode", B)):
+        streams = torch.randn(rows, S, W, device=dev)
+        one = torch.randn(rows, W, device=dev)
+        y = torch.randn(rows, W, device=dev).to(bf)
+        w_ = torch.ones(W, device=dev)
+        mix, wo, wi = torch.eye(S, device=dev), torch.ones(S, device=dev), torch.full((S,), 1.0 / S, device=dev)
+        o = torch.empty(rows, W, dtype=bf, device=dev)
+        ms = timed(lambda: ops.hyper_norm(o, streams, y, mix, wo, wi, w_, 1e-6), flush)
+        ms_r = timed(lambda: ops.rmsnorm_stream(o, one, y, None, w_, 1e-6, False), flush)
+        out[f"stream_copies_norm_{name}"] = {"us": round(ms * 1e3, 1), "frac_of_hbm": frac(rows * W * (8.0 * S + 4), ms),
+                                             "beside_stream_norm_us": round(ms_r * 1e3, 1),
+                                             "beside_frac_of_hbm": frac(rows * W * 12.0, ms_r)}
+
+    pages = B * (-(-(ctx + 1) // page)) + -(-T // page) + 2
+    width = -(-max(ctx + 1, T) // page)
+    kc = torch.randn(pages, G, page, D, device=dev).to(bf)
+    vc = torch.randn(pages, G, page, D, device=dev).to(bf)
+    # rotation of neighbouring pairs + cache write, beside the rotation by halves with the per-head norm
+    freq = (500000.0 ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot)).float().to(dev)
+    n_left = (2 * H + 2 * G) * D                             # q | k | v | gate
+    for name, rows in (("prefill", T), ("decode", B)):
+        proj = torch.randn(rows, n_left, device=dev).to(bf)
+        pos = i32(list(range(rows)))
+        slots = i32(list(range(page, page + rows)))
+        ms = timed(lambda: ops.rope_pairs_write(proj, H * D, (H + G) * D, pos, freq, 1.0, rot, kc, vc, slots, H, G, D, D, page), flush)
+        byts = rows * (2 * H * D + 2 * 2 * G * D) * 2.0
+        ms_h = timed(lambda: ops.rope_headnorm_write(proj, H * D, (H + G) * D, pos, freq, rot, 1e-6, kc, vc, slots, H, G, D, D, page), flush)
+        out[f"rotate_pairs_write_{name}"] = {"us": round(ms * 1e3, 1), "frac_of_hbm": frac(byts, ms),
+                                             "beside_rotation_by_halves_us": round(ms_h * 1e3, 1), "beside_frac_of_hbm": frac(byts, ms_h)}
+
+    # attention with a sink (no blocks of positions), then the output gate
+    sinks = torch.zeros(H, device=dev)
+    for name, reqs, per, seq in (("prefill", 1, T, T), ("decode", B, 1, ctx + 1)):
+        rows = reqs * per
+        q = torch.randn(rows, H, D, device=dev).to(bf)
+        o = torch.empty(rows, H, D, dtype=bf, device=dev)
+        gate = torch.randn(rows, H * D, device=dev).to(bf)
+        heads = torch.empty(rows, H * D, dtype=bf, device=dev)
+        bt = torch.zeros(reqs, width, dtype=torch.int32, device=dev)
+        n = -(-seq // page)
+        for r in range(reqs):
+            bt[r, :n] = torch.arange(1 + r * n, 1 + (r + 1) * n, dtype=torch.int32, device=dev)
+        step = SimpleNamespace(q_start=i32([i * per for i in range(reqs + 1)]), seq_lens=i32([seq] * reqs), num_requests=reqs,
+                               num_decode=reqs if per == 1 else 0, max_q_len=per, max_seq_len=seq)
+        ms = timed(lambda: ops.attention_biased(o, q, kc, vc, bt, step, G, page, D ** -0.5, 0.0, None, None, chunk=None, sinks=sinks), flush)
+        ms_g = timed(lambda: ops.gate_mul(heads, o.view(rows, H * D), gate, "sigmoid", 0.8), flush)
+        seen = sum(i + 1 for i in range(seq - per, seq))
+        flops = 4.0 * D * H * seen * reqs
+        byts = reqs * seq * G * 2 * D * 2.0 + rows * H * D * 4.0
+        out[f"sink_attention_{name}"] = {"us": round(ms * 1e3, 1), "tflops": round(flops / ms / 1e9, 1),
+                                         "frac_of_bf16": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 3),
+                                         "frac_of_hbm": frac(byts, ms), "gate_us": round(ms_g * 1e3, 1),
+                                         "gate_frac_of_hbm": frac(rows * H * D * 6.0, ms_g)}
+
+    # the state-space mixer: prepare (filter, SiLU, dt, decay) and scan, beside the linear attention's scan at the same
+    # number of state values a layer
+    SH, P, N, SG, taps, parts = z["sheads"], z["sdim"], z["state"], z["sgroups"], z["taps"], z["parts"]
+    inner, channels = SH * P, SH * P + 2 * SG * N
+    n_in = 2 * inner + 2 * SG * N + SH
+    conv_w, conv_b = torch.randn(channels, taps, device=dev) * 0.3, torch.zeros(channels, device=dev)
+    a_log, dt_bias, skip = torch.zeros(SH, device=dev), torch.zeros(SH, device=dev), torch.ones(SH, device=dev)
+    norm_w = torch.ones(inner, device=dev)
+    LH = z["lheads"]
+    decay = torch.full((LH,), 0.99, device=dev)
+    for name, reqs, per in (("prefill", 1, T), ("decode", B, 1)):
+        rows = reqs * per
+        proj = torch.randn(rows, n_in, device=dev).to(bf)
+        state = torch.zeros(reqs + 1, SH * N * P + (taps - 1) * channels, device=dev)
+        step = SimpleNamespace(q_start=i32([i * per for i in range(reqs + 1)]), state_slots=i32(list(range(reqs))), num_requests=reqs,
+                               token_request=i32([r for r in range(reqs) for _ in range(per)]), max_q_len=per)
+        ready = torch.empty(rows, channels + 2 * SH, device=dev)
+        y = torch.empty(rows, inner, device=dev)
+        g_ = torch.empty(rows, inner, dtype=bf, device=dev)
+        ms_p = timed(lambda: ops.ssm_prepare(ready, proj, inner, inner + channels, conv_w, conv_b, a_log, dt_bias, state, SH * N * P,
+                                             step, SH, channels, taps), flush)
+        ms_s = timed(lambda: ops.ssm_scan(y, ready, proj, inner, state, skip, step, SH, SG, N, P, taps), flush)
+        ms_n = timed(lambda: ops.gated_group_rmsnorm(g_, y, proj[:, :inner], norm_w, 1e-6, parts, "silu", True), flush)
+        flops = 5.0 * rows * SH * N * P                       # decay, write (two), read (two) a state value
+        # the linear attention of the paired mixer (and of Komirax): D x D states
+        lproj = torch.randn(rows, 4 * LH * D, device=dev).to(bf)
+        lstate = torch.zeros(reqs + 1, LH, D, D, device=dev)
+        lo = torch.empty(rows, LH * D, device=dev)
+        ms_l = timed(lambda: ops.lightning(lo, lproj, lstate, decay, step, LH, D, D), flush)
+        lflops = 5.0 * rows * LH * D * D
+        lg = torch.empty(rows, LH * D, dtype=bf, device=dev)
+        lw = torch.ones(LH * D, device=dev).to(bf)
+        ms_ln = timed(lambda: ops.gated_rmsnorm(lg, lo, lproj[:, 3 * LH * D:], lw, 1e-6), flush)
+        out[f"state_space_{name}"] = {
+            "prepare_us": round(ms_p * 1e3, 1), "prepare_frac_of_hbm": frac(rows * (channels * 2.0 + (channels + 2 * SH) * 4.0), ms_p),
+            "scan_us": round(ms_s * 1e3, 1), "scan_tflops_fp32": round(flops / ms_s / 1e9, 2),
+            "scan_frac_of_fp32_nominal": round(flops / (ms_s / 1e3) / FP32_PEAK, 3),
+            "scan_frac_of_hbm": frac(reqs * SH * N * P * 8.0 + rows * (channels + inner) * 4.0, ms_s),
+            "gated_norm_us": round(ms_n * 1e3, 1), "gated_norm_frac_of_hbm": frac(rows * inner * 8.0, ms_n),
+            "beside_linear_attention_scan_us": round(ms_l * 1e3, 1), "beside_scan_tflops_fp32": round(lflops / ms_l / 1e9, 2),
+            "beside_scan_frac_of_fp32_nominal": round(lflops / (ms_l / 1e3) / FP32_PEAK, 3),
+            "beside_scan_frac_of_hbm": frac(reqs * LH * D * D * 8.0 + rows * LH * D * (3 * 2.0 + 4.0), ms_l),
+            "beside_gated_norm_us": round(ms_ln * 1e3, 1), "beside_gated_norm_frac_of_hbm": frac(rows * LH * D * 8.0, ms_ln)}
+
+    # the gated dense feed-forward's activation beside the SiLU one
+    ff = z["ff"]
+    for name, rows in (("prefill", T), ("decode", B)):
+        gu = torch.randn(rows, 2 * ff, device=dev).to(bf)
+        a_ = torch.empty(rows, ff, dtype=bf, device=dev)
+        ms = timed(lambda: ops.act_mul(a_, gu, "gelu_tanh", 64), flush)
+        ms_q = timed(lambda: ops.silu_mul(a_, gu, 64), flush)
+        out[f"gelu_gate_{name}"] = {"us": round(ms * 1e3, 1), "frac_of_hbm": frac(rows * ff * 6.0, ms),
+                                    "beside_silu_us": round(ms_q * 1e3, 1), "beside_frac_of_hbm": frac(rows * ff * 6.0, ms_q)}
+    return out
+
+
 def run_design(a) -> dict:
     """``--design komirax``: prefill and decode throughput of Komirax layers beside Qwen2 layers of the same
     width and count (random weights, bfloat16, through the step function), and each new kernel alone."""
@@ -1051,6 +1212,28 @@ def run_design(a) -> dict:
             if "kernels" in a.phases.split(","):
                 entry["kernels"] = vofinex_kernels(ops, z, pk, T, B, ctx, page)
                 entry["komirax_kernels"] = komirax_kernels(ops, KOMIRAX_SIZES[z["beside"]], pk, T, B, ctx, page)
+            result["sizes"][name] = entry
+            continue
+        if a.design == "gugezen":
+            # beside Komirax layers of the same width and about the same weight count, the closest design the engine has (a
+            # 32-bit stream, linear attention with a decaying state, an attention of its own, dense and routed feed-forwards)
+            z = GUGEZEN_SIZES[name]
+            eng = build_engine_on_device(f"gugezen-{name}", 4 * groups, ctx_len=ctx_len, page=page, max_seqs=B,
+                                         max_tokens=max(T, ctx), graph_sizes=(B,), mcfg=gugezen_config(z, groups, vocab))
+            ours = measure(eng)
+            del eng
+            torch.cuda.empty_cache()
+            eng = build_engine_on_device(f"komirax-{z['beside']}", 4 * groups, ctx_len=ctx_len, page=page, max_seqs=B,
+                                         max_tokens=max(T, ctx), graph_sizes=(B,),
+                                         mcfg=komirax_config(KOMIRAX_SIZES[z["beside"]], groups, vocab))
+            beside = measure(eng)
+            del eng
+            torch.cuda.empty_cache()
+            entry = {"layers": 4 * groups, "width": z["width"], "gugezen": ours, "beside": f"komirax-{z['beside']}", "komirax": beside,
+                     "prefill_ratio": round(ours["prefill_tok_s"] / beside["prefill_tok_s"], 3),
+                     "decode_ratio": round(ours["decode_tok_s"] / beside["decode_tok_s"], 3)}
+            if "kernels" in a.phases.split(","):
+                entry["kernels"] = gugezen_kernels(ops, z, pk, T, B, ctx, page)
             result["sizes"][name] = entry
             continue
         if a.design == "pizunex":
@@ -1182,7 +1365,7 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--phases", default="prefill,decode,points,e2e,kernels,mixed",
                     help="which measurements to run (decode always runs); fewer for a profiler capture")
-    ap.add_argument("--design", default="", choices=["", "komirax", "pizunex", "vofinex"],
+    ap.add_argument("--design", default="", choices=["", "komirax", "pizunex", "vofinex", "gugezen"],
                     help="instead of the default workload: layers of this design beside layers of the closest other one (Komirax "
                          "beside Qwen2, Pizunex beside Komirax) at the same width "
                          "(prefill and decode throughput, and each of the design's kernels alone)")
