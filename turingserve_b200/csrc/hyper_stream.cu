@@ -92,12 +92,115 @@ hyper_norm_kernel(T* __restrict__ out, float* __restrict__ streams, const T* __r
     out[row * hidden + i] = from_f<T>(u_s[i] * rstd * w[i]);
 }
 
+
+// The same for rows a multiple of 4 long and at most 4 * CH * blockDim: every load of a thread (its 16 bytes of every
+// copy, of y or of its partial sums) is issued before the first is used, the new copies and u stay in registers, the
+// stream moves as float4: one round trip to memory.
+template <typename T, int S, int CH>
+__global__ void __launch_bounds__(256)
+hyper_norm_vec_kernel(T* __restrict__ out, float* __restrict__ streams, const T* __restrict__ y,
+                      const float* __restrict__ part, int splits, size_t split_stride, const T* __restrict__ bias,
+                      const float* __restrict__ mix_w, const float* __restrict__ out_w, const float* __restrict__ in_w,
+                      const float* __restrict__ w, float eps, int hidden, int first, float alpha) {
+  pdl_launch_dependents();
+  __shared__ float scratch[32];
+  __shared__ HsWeights hw;
+  if (threadIdx.x < S * S) hw.mix[threadIdx.x] = mix_w != nullptr ? mix_w[threadIdx.x] : (threadIdx.x / S == threadIdx.x % S ? 1.f : 0.f);
+  if (threadIdx.x < S) {
+    hw.out[threadIdx.x] = out_w != nullptr ? out_w[threadIdx.x] : 1.f;
+    hw.in[threadIdx.x] = in_w != nullptr ? in_w[threadIdx.x] : 1.f;
+  }
+  pdl_wait();
+  __syncthreads();
+  const size_t row = blockIdx.x;
+  float* xs = streams + row * S * hidden;
+  const bool has_y = y != nullptr || part != nullptr;
+  float u[CH][4];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int i = (c * blockDim.x + threadIdx.x) * 4;
+    if (i < hidden) {
+      float yv[4] = {0.f, 0.f, 0.f, 0.f};
+      if (part != nullptr) {
+        float4 p4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int sp = 0; sp < splits; ++sp) {
+          const float4 q4 = __ldcg(reinterpret_cast<const float4*>(part + (size_t)sp * split_stride + row * hidden + i));
+          p4.x += q4.x; p4.y += q4.y; p4.z += q4.z; p4.w += q4.w;
+        }
+        const float pv[4] = {p4.x, p4.y, p4.z, p4.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) yv[k] = round_to<T>(pv[k] + (bias != nullptr ? to_f(bias[i + k]) : 0.f));
+      } else if (y != nullptr) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) yv[k] = to_f(y[row * hidden + i + k]);
+      }
+      float x[S][4], nx[S][4];
+      if (!first) {
+#pragma unroll
+        for (int s = 0; s < S; ++s) {
+          const float4 v = *reinterpret_cast<const float4*>(xs + (size_t)s * hidden + i);
+          x[s][0] = v.x; x[s][1] = v.y; x[s][2] = v.z; x[s][3] = v.w;
+        }
+      }
+#pragma unroll
+      for (int t = 0; t < S; ++t) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          if (first) nx[t][k] = alpha * yv[k];
+          else if (has_y) {
+            float a = 0.f;
+#pragma unroll
+            for (int s = 0; s < S; ++s) a = fmaf(hw.mix[s * S + t], x[s][k], a);
+            nx[t][k] = fmaf(hw.out[t], yv[k], a);
+          } else nx[t][k] = x[t][k];
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) u[c][k] = 0.f;
+#pragma unroll
+      for (int t = 0; t < S; ++t) {
+        if (first || has_y) *reinterpret_cast<float4*>(xs + (size_t)t * hidden + i) = make_float4(nx[t][0], nx[t][1], nx[t][2], nx[t][3]);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) u[c][k] = fmaf(hw.in[t], nx[t][k], u[c][k]);
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) ss = fmaf(u[c][k], u[c][k], ss);
+    }
+  }
+  if (out == nullptr) return;
+  ss = block_sum(ss, scratch);
+  const float rstd = 1.f / sqrtf(ss / (float)hidden + eps);
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int i = (c * blockDim.x + threadIdx.x) * 4;
+    if (i < hidden) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) out[row * hidden + i + k] = from_f<T>(u[c][k] * rstd * w[i + k]);
+    }
+  }
+}
+
 template <typename T>
 int launch_hyper(int S, dim3 grid, dim3 block, size_t smem, cudaStream_t s, T* out, float* streams, const T* y,
                  const float* part, int splits, size_t split_stride, const T* bias, const float* mix_w,
                  const float* out_w, const float* in_w, const float* w, float eps, int hidden, int first, float alpha) {
+  // rows a multiple of 4 long on 16-byte boundaries, up to 4 copies: the kernel that keeps the row in registers
+  const bool vec = S <= 4 && hidden % 4 == 0 && hidden <= 4 * 4 * 256 && !((uintptr_t)streams & 15) && !((uintptr_t)part & 15);
+  const int ch = hidden <= 1024 ? 1 : (hidden <= 2048 ? 2 : 4);
+  const dim3 vblock((((hidden / 4 + ch - 1) / ch) + 31) / 32 * 32);
+#define TS_HV(N, CH)                                                                                                  \
+  ts_launch(hyper_norm_vec_kernel<T, N, CH>, grid, vblock, 0, s, out, streams, y, part, splits, split_stride, bias, mix_w, \
+            out_w, in_w, w, eps, hidden, first, alpha)
 #define TS_HS(N)                                                                                                      \
   case N:                                                                                                             \
+    if (vec && N <= 4) {                                                                                              \
+      constexpr int M = N <= 4 ? N : 1;                                                                               \
+      if (ch == 1) TS_HV(M, 1);                                                                                       \
+      else if (ch == 2) TS_HV(M, 2);                                                                                  \
+      else TS_HV(M, 4);                                                                                               \
+      break;                                                                                                          \
+    }                                                                                                                 \
     if (smem > 48 * 1024) cudaFuncSetAttribute(hyper_norm_kernel<T, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     ts_launch(hyper_norm_kernel<T, N>, grid, block, smem, s, out, streams, y, part, splits, split_stride, bias, mix_w, \
               out_w, in_w, w, eps, hidden, first, alpha);                                                             \
@@ -107,6 +210,7 @@ int launch_hyper(int S, dim3 grid, dim3 block, size_t smem, cudaStream_t s, T* o
     default: return -1;
   }
 #undef TS_HS
+#undef TS_HV
   return 0;
 }
 

@@ -32,38 +32,82 @@ __device__ __forceinline__ void ss_cp_async_4(void* smem, const void* gmem) {
 }
 __device__ __forceinline__ float ss_softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
-// grid (T, ceil((Cn + H) / blockDim)): a thread a channel (or a head's dt and a)
+// grid (ceil(T / SS_PREP_TOKENS), ceil((Cn + H) / blockDim)): a thread takes one channel (or one head's dt and a) of
+// SS_PREP_TOKENS neighbouring tokens.  The tokens' raw inputs are all loaded before the first is used; the filter's
+// window slides through registers, and is refilled (from the rows before, or from the slot's memory where they lie before
+// the step's first token) only at the first token of the thread and where another request begins.
+constexpr int SS_PREP_TOKENS = 8;
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 ssm_prepare_kernel(float* __restrict__ ready, const T* __restrict__ proj, int proj_stride, int xbc_off, int dt_off,
                    const float* __restrict__ conv_w, const float* __restrict__ conv_b, const float* __restrict__ a_log,
                    const float* __restrict__ dt_bias, const float* __restrict__ state, size_t state_stride,
                    size_t tail_off, const int* __restrict__ token_request, const int* __restrict__ q_start,
-                   const int* __restrict__ slots, int H, int Cn, int taps) {
+                   const int* __restrict__ slots, int T_, int H, int Cn, int taps) {
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x;
+  const int t_base = blockIdx.x * SS_PREP_TOKENS;
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= Cn + H) return;
   const int W = Cn + 2 * H;
-  float* out = ready + (size_t)t * W;
+  const int count = min(SS_PREP_TOKENS, T_ - t_base);
   if (c >= Cn) {
     const int h = c - Cn;
-    const float dt = ss_softplus(to_f(proj[(size_t)t * proj_stride + dt_off + h]) + dt_bias[h]);
-    out[Cn + h] = dt;
-    out[Cn + H + h] = expf(-expf(a_log[h]) * dt);
+    const float bias = dt_bias[h], rate = expf(a_log[h]);
+    for (int k = 0; k < count; ++k) {
+      const int t = t_base + k;
+      const float dt = ss_softplus(to_f(proj[(size_t)t * proj_stride + dt_off + h]) + bias);
+      ready[(size_t)t * W + Cn + h] = dt;
+      ready[(size_t)t * W + Cn + H + h] = expf(-rate * dt);
+    }
     return;
   }
-  const int b = token_request[t];
-  const int t0 = q_start[b], i = t - t0;
-  const float* tail = state + (size_t)slots[b] * state_stride + tail_off;       // [taps - 1][Cn]
-  float acc = conv_b != nullptr ? conv_b[c] : 0.f;
-  for (int u = 0; u < taps; ++u) {
-    const int rel = i - (taps - 1) + u;                // the input's place, counted from the step's first token
-    const float x = rel >= 0 ? to_f(proj[(size_t)(t0 + rel) * proj_stride + xbc_off + c]) : tail[(size_t)(rel + taps - 1) * Cn + c];
-    acc = fmaf(conv_w[c * taps + u], x, acc);
+  float x[SS_PREP_TOKENS];
+#pragma unroll
+  for (int k = 0; k < SS_PREP_TOKENS; ++k)
+    x[k] = k < count ? to_f(proj[(size_t)(t_base + k) * proj_stride + xbc_off + c]) : 0.f;
+  float wgt[SS_MAX_TAPS];
+#pragma unroll
+  for (int u = 0; u < SS_MAX_TAPS; ++u) wgt[u] = u < taps ? conv_w[c * taps + u] : 0.f;
+  const float bias = conv_b != nullptr ? conv_b[c] : 0.f;
+  const int keep = taps - 1;
+  float win[SS_MAX_TAPS - 1];                          // the inputs before the present token, oldest first (keep of them)
+#pragma unroll
+  for (int k = 0; k < SS_PREP_TOKENS; ++k) {
+    if (k < count) {
+      const int t = t_base + k;
+      const int b = token_request[t];
+      const int t0 = q_start[b], i = t - t0;
+      if (k == 0 || i == 0) {
+        const float* tail = state + (size_t)slots[b] * state_stride + tail_off;       // [taps - 1][Cn]
+#pragma unroll
+        for (int u = 0; u < SS_MAX_TAPS - 1; ++u) {
+          if (u < keep) {
+            const int rel = i - keep + u;              // the input's place, counted from the step's first token
+            win[u] = rel >= 0 ? to_f(proj[(size_t)(t0 + rel) * proj_stride + xbc_off + c]) : tail[(size_t)(rel + keep) * Cn + c];
+          }
+        }
+      }
+      float acc = bias;
+#pragma unroll
+      for (int u = 0; u < SS_MAX_TAPS - 1; ++u)
+        if (u < keep) acc = fmaf(wgt[u], win[u], acc);
+      // (the present token's weight is the last of its taps; the index is not known at compile time)
+      float w_now = wgt[0];
+#pragma unroll
+      for (int u = 1; u < SS_MAX_TAPS; ++u)
+        if (u == keep) w_now = wgt[u];
+      acc = fmaf(w_now, x[k], acc);
+      ready[(size_t)t * W + c] = acc / (1.f + expf(-acc));
+#pragma unroll
+      for (int u = 0; u < SS_MAX_TAPS - 2; ++u)
+        if (u + 1 < keep) win[u] = win[u + 1];
+#pragma unroll
+      for (int u = 0; u < SS_MAX_TAPS - 1; ++u)
+        if (u == keep - 1) win[u] = x[k];
+    }
   }
-  out[c] = acc / (1.f + expf(-acc));
 }
 
 template <typename T>
@@ -216,11 +260,11 @@ TS_API int ts_ssm_prepare(float* ready, const void* proj, int proj_stride, int x
   if (T <= 0) return 0;
   if (taps < 1 || taps > SS_MAX_TAPS) TS_REFUSE(TS_ERR_LIMIT, "ts_ssm_prepare: a filter of %d taps (1 to %d)", taps, SS_MAX_TAPS);
   cudaStream_t s = (cudaStream_t)stream;
-  dim3 grid(T, ceil_div(Cn + H, 256));
+  dim3 grid(ceil_div(T, SS_PREP_TOKENS), ceil_div(Cn + H, 256));
   if (grid.y > 65535) TS_REFUSE(TS_ERR_LIMIT, "ts_ssm_prepare: %d channels", Cn);
 #define TS_SP(TT)                                                                                                     \
   ts_launch(ssm_prepare_kernel<TT>, grid, dim3(256), 0, s, ready, (const TT*)proj, proj_stride, xbc_off, dt_off, conv_w, \
-            conv_b, a_log, dt_bias, state, (size_t)state_stride, (size_t)tail_off, token_request, q_start, slots, H, Cn, taps)
+            conv_b, a_log, dt_bias, state, (size_t)state_stride, (size_t)tail_off, token_request, q_start, slots, T, H, Cn, taps)
   if (dtype == TS_F32) TS_SP(float);
   else if (dtype == TS_BF16) TS_SP(bf16);
   else TS_REFUSE(TS_ERR_DTYPE, "ts_ssm_prepare: dtype %d", dtype);
