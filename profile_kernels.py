@@ -356,6 +356,73 @@ def fused_step(a) -> None:
     print(f"  a layer: {(leave[:, 5 * L].max() - leave[:, 5].max()) / mhz / (L - 1):.2f} us")
 
 
+def design_step(a) -> None:
+    """One step of ``--layers`` layers of another design at one of its measured sizes (``bench.py --design``): a prompt of
+    ``--prefill`` tokens, or ``--batch`` single tokens at ``--context`` launched kernel by kernel; the duration of every
+    kernel (CUPTI through torch.profiler) summed per kernel, and the step's own time from CUDA events without the profiler.
+    Also the workload the designs' kernels are captured on under ncu."""
+    import collections
+    import re
+
+    import numpy as np
+    from torch.profiler import ProfilerActivity, profile
+
+    import bench
+    from turingserve_b200.engine.batch import StepEntry
+
+    sizes = getattr(bench, f"{a.design.upper()}_SIZES")[a.size]
+    groups = max(1, a.layers // 4)
+    vocab = 32768
+    T, B, ctx = a.prefill, a.batch, a.context
+    mcfg = getattr(bench, f"{a.design}_config")(sizes, groups, vocab)
+    eng = bench.build_engine_on_device(f"{a.design}-{a.size}", 4 * groups, ctx_len=max(T, ctx) + 128, page=a.page, max_seqs=B,
+                                       max_tokens=max(T, ctx), graph_sizes=(), mcfg=mcfg)
+    runner, cache = eng.runner, eng.cache
+    rng = np.random.default_rng(0)
+    if T:
+        toks = rng.integers(0, vocab, size=T).tolist()
+
+        def once(i=0):
+            rc = cache.admit("p")
+            runner.step([StepEntry(rc, toks, [T - 1])])
+            cache.release(rc)
+    else:
+        rcs = [cache.admit(f"d{i}") for i in range(B)]
+        for rc in rcs:
+            runner.step([StepEntry(rc, rng.integers(0, vocab, size=ctx).tolist(), [])])
+
+        def once(i=0):
+            runner.step([StepEntry(rc, [int(rng.integers(0, vocab))], [0]) for rc in rcs])
+
+    for _ in range(3):
+        once()
+    if a.plain:                                       # (under ncu: the steps alone, no second user of CUPTI)
+        torch.cuda.synchronize()
+        return
+    us = timed(once, 5)
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        once()
+        torch.cuda.synchronize()
+    evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA]
+
+    def short(name: str) -> str:
+        m = re.search(r"(gemm_pair_kernel<[^>]*>|gemm_tc_kernel<[^>]*>|\w+_kernel|Memcpy \w+|nvjet\w*)", name)
+        return m.group(1) if m else name[:50]
+
+    share = collections.OrderedDict()
+    for e in evs:
+        d = e.time_range.end - e.time_range.start
+        share.setdefault(short(e.name), [0, 0.0])
+        share[short(e.name)][0] += 1
+        share[short(e.name)][1] += d
+    total = sum(d for _, d in share.values())
+    what = f"prompt of {T} tokens" if T else f"{B} single tokens at context {ctx}"
+    print(f"{a.design}-{a.size}, {4 * groups} layers, {what}, page {a.page}: one step = {us:.1f} us (CUDA events, launched kernel "
+          f"by kernel), kernel durations add up to {total:.1f} us, {len(evs)} kernels and copies")
+    for n, (c, d) in sorted(share.items(), key=lambda kv: -kv[1][1]):
+        print(f"  {d:8.1f} us  {c:4d} x {d / c:7.2f}  {n}")
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(prog="python profile_kernels.py")
     ap.add_argument("--model", default="qwen2.5-1.5b", choices=sorted(SHAPES), help="whose layer sizes to use")
@@ -392,12 +459,21 @@ def main() -> int:
     s.add_argument("--context", type=int, default=2048)
     s.add_argument("--layers", type=int, default=4)
     s.add_argument("--page", type=int, default=PAGE)
+    s = sub.add_parser("design_step")
+    s.add_argument("--design", default="gugezen", choices=["komirax", "pizunex", "vofinex", "gugezen"])
+    s.add_argument("--size", default="1.5b")
+    s.add_argument("--layers", type=int, default=4)
+    s.add_argument("--prefill", type=int, default=0, help="a prompt of this many tokens (0: single tokens)")
+    s.add_argument("--plain", action="store_true", help="three steps and nothing else (the workload of an ncu capture)")
+    s.add_argument("--batch", type=int, default=8)
+    s.add_argument("--context", type=int, default=2048)
+    s.add_argument("--page", type=int, default=PAGE)
     a = ap.parse_args()
     global H, KVH, D, LAYERS, SHAPE
     SHAPE = SHAPES[a.model]
     H, KVH, D, LAYERS = SHAPE["num_heads"], SHAPE["num_kv_heads"], SHAPE["head_dim"], SHAPE["num_layers"]
     {"decode_attention": decode_attention, "prefill_attention": prefill_attention, "gemm": gemm,
-     "timeline": timeline, "fused_step": fused_step}[a.workload](a)
+     "timeline": timeline, "fused_step": fused_step, "design_step": design_step}[a.workload](a)
     return 0
 
 

@@ -159,8 +159,22 @@ lightning_kernel(float* __restrict__ out, const T* __restrict__ proj, int proj_s
 
 // proj: [T, proj_stride] rows holding q at column 0, k at H D, v at 2 H D.  state: [slots, H, D, V] 32-bit.
 // decay: [H] 32-bit on the device.  out: [T, H V] 32-bit.
+// longest: the most tokens a request brings (0: not known); from LT_LATE_TOKENS on the kernel is launched late (see
+// ts_launch_late).
+constexpr int LT_LATE_TOKENS = 64;
+
+TS_API int ts_lightning_ex(float* out, const void* proj, int proj_stride, float* state, const float* decay,
+                           const int* q_start, const int* slots, int B, int H, int D, int V, int longest, int dtype,
+                           void* stream);
+
 TS_API int ts_lightning(float* out, const void* proj, int proj_stride, float* state, const float* decay,
                         const int* q_start, const int* slots, int B, int H, int D, int V, int dtype, void* stream) {
+  return ts_lightning_ex(out, proj, proj_stride, state, decay, q_start, slots, B, H, D, V, 0, dtype, stream);
+}
+
+TS_API int ts_lightning_ex(float* out, const void* proj, int proj_stride, float* state, const float* decay,
+                           const int* q_start, const int* slots, int B, int H, int D, int V, int longest, int dtype,
+                           void* stream) {
   if (B <= 0) return 0;
   if (H <= 0 || D <= 0 || V <= 0) TS_REFUSE(TS_ERR_SHAPE, "ts_lightning: %d heads of %d x %d", H, D, V);
   const int parts = ceil_div(D, LT_ROWS);
@@ -182,8 +196,12 @@ TS_API int ts_lightning(float* out, const void* proj, int proj_stride, float* st
       if (e != cudaSuccess) TS_REFUSE((int)e, "ts_lightning: shared memory %zu: %s", smem, cudaGetErrorString(e)); \
       configured = smem;                                                                                            \
     }                                                                                                               \
-    ts_launch(lightning_kernel<TT>, dim3(grid), dim3(parts * LT_COLS), smem, s, out, (const TT*)proj, proj_stride, \
-              state, decay, q_start, slots, H, D, V, parts, fast_rows);                                                        \
+    if (longest >= LT_LATE_TOKENS)                                                                                  \
+      ts_launch_late(lightning_kernel<TT>, dim3(grid), dim3(parts * LT_COLS), smem, s, out, (const TT*)proj, proj_stride, \
+                     state, decay, q_start, slots, H, D, V, parts, fast_rows);                                      \
+    else                                                                                                            \
+      ts_launch(lightning_kernel<TT>, dim3(grid), dim3(parts * LT_COLS), smem, s, out, (const TT*)proj, proj_stride, \
+                state, decay, q_start, slots, H, D, V, parts, fast_rows);                                           \
   } while (0)
   if (dtype == TS_F32) TS_LT(float);
   else if (dtype == TS_BF16) TS_LT(bf16);

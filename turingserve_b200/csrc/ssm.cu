@@ -38,7 +38,9 @@ __device__ __forceinline__ float ss_softplus(float x) { return x > 20.f ? x : lo
 // the step's first token) only at the first token of the thread and where another request begins.
 constexpr int SS_PREP_TOKENS = 8;
 
-template <typename T>
+// (SS_PREP_TOKENS_ = 1 for steps of few tokens, where every token is likely a request of its own and the launch has
+// few threads as it is; the arithmetic of a token is the same in both instances, bit for bit)
+template <typename T, int SS_PREP_TOKENS_>
 __global__ void __launch_bounds__(256)
 ssm_prepare_kernel(float* __restrict__ ready, const T* __restrict__ proj, int proj_stride, int xbc_off, int dt_off,
                    const float* __restrict__ conv_w, const float* __restrict__ conv_b, const float* __restrict__ a_log,
@@ -47,11 +49,11 @@ ssm_prepare_kernel(float* __restrict__ ready, const T* __restrict__ proj, int pr
                    const int* __restrict__ slots, int T_, int H, int Cn, int taps) {
   pdl_launch_dependents();
   pdl_wait();
-  const int t_base = blockIdx.x * SS_PREP_TOKENS;
+  const int t_base = blockIdx.x * SS_PREP_TOKENS_;
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= Cn + H) return;
   const int W = Cn + 2 * H;
-  const int count = min(SS_PREP_TOKENS, T_ - t_base);
+  const int count = min(SS_PREP_TOKENS_, T_ - t_base);
   if (c >= Cn) {
     const int h = c - Cn;
     const float bias = dt_bias[h], rate = expf(a_log[h]);
@@ -63,9 +65,9 @@ ssm_prepare_kernel(float* __restrict__ ready, const T* __restrict__ proj, int pr
     }
     return;
   }
-  float x[SS_PREP_TOKENS];
+  float x[SS_PREP_TOKENS_];
 #pragma unroll
-  for (int k = 0; k < SS_PREP_TOKENS; ++k)
+  for (int k = 0; k < SS_PREP_TOKENS_; ++k)
     x[k] = k < count ? to_f(proj[(size_t)(t_base + k) * proj_stride + xbc_off + c]) : 0.f;
   float wgt[SS_MAX_TAPS];
 #pragma unroll
@@ -74,7 +76,7 @@ ssm_prepare_kernel(float* __restrict__ ready, const T* __restrict__ proj, int pr
   const int keep = taps - 1;
   float win[SS_MAX_TAPS - 1];                          // the inputs before the present token, oldest first (keep of them)
 #pragma unroll
-  for (int k = 0; k < SS_PREP_TOKENS; ++k) {
+  for (int k = 0; k < SS_PREP_TOKENS_; ++k) {
     if (k < count) {
       const int t = t_base + k;
       const int b = token_request[t];
@@ -260,23 +262,34 @@ TS_API int ts_ssm_prepare(float* ready, const void* proj, int proj_stride, int x
   if (T <= 0) return 0;
   if (taps < 1 || taps > SS_MAX_TAPS) TS_REFUSE(TS_ERR_LIMIT, "ts_ssm_prepare: a filter of %d taps (1 to %d)", taps, SS_MAX_TAPS);
   cudaStream_t s = (cudaStream_t)stream;
-  dim3 grid(ceil_div(T, SS_PREP_TOKENS), ceil_div(Cn + H, 256));
+  const bool few = T <= 64;
+  dim3 grid(few ? T : ceil_div(T, SS_PREP_TOKENS), ceil_div(Cn + H, 256));
   if (grid.y > 65535) TS_REFUSE(TS_ERR_LIMIT, "ts_ssm_prepare: %d channels", Cn);
-#define TS_SP(TT)                                                                                                     \
-  ts_launch(ssm_prepare_kernel<TT>, grid, dim3(256), 0, s, ready, (const TT*)proj, proj_stride, xbc_off, dt_off, conv_w, \
+#define TS_SP1(TT, N)                                                                                                 \
+  ts_launch(ssm_prepare_kernel<TT, N>, grid, dim3(256), 0, s, ready, (const TT*)proj, proj_stride, xbc_off, dt_off, conv_w, \
             conv_b, a_log, dt_bias, state, (size_t)state_stride, (size_t)tail_off, token_request, q_start, slots, T, H, Cn, taps)
+#define TS_SP(TT)                     \
+  do {                                \
+    if (few) TS_SP1(TT, 1);           \
+    else TS_SP1(TT, SS_PREP_TOKENS);  \
+  } while (0)
   if (dtype == TS_F32) TS_SP(float);
   else if (dtype == TS_BF16) TS_SP(bf16);
   else TS_REFUSE(TS_ERR_DTYPE, "ts_ssm_prepare: dtype %d", dtype);
 #undef TS_SP
+#undef TS_SP1
   TS_LAUNCH_CHECK();
 }
 
 // out [T, H P] 32-bit; ready as ts_ssm_prepare left it; skip [H] 32-bit (D, may be null); state [slots, state_stride]:
 // [H N P | (taps - 1) x Cn], read and left updated at each request's slot.
+// longest: the most tokens a request brings (0: not known); from SS_LATE_TOKENS on the kernel is launched late (see
+// ts_launch_late).
+constexpr int SS_LATE_TOKENS = 64;
+
 TS_API int ts_ssm_scan(float* out, const float* ready, const void* proj, int proj_stride, int xbc_off, float* state,
                        long long state_stride, const float* skip, const int* q_start, const int* slots, int B, int H,
-                       int G, int N, int P, int taps, int dtype, void* stream) {
+                       int G, int N, int P, int taps, int longest, int dtype, void* stream) {
   if (B <= 0) return 0;
   if (H <= 0 || G <= 0 || H % G || N <= 0 || P <= 0) TS_REFUSE(TS_ERR_SHAPE, "ts_ssm_scan: %d heads in %d groups, state %d x %d", H, G, N, P);
   if (taps < 1 || taps > SS_MAX_TAPS) TS_REFUSE(TS_ERR_LIMIT, "ts_ssm_scan: a filter of %d taps (1 to %d)", taps, SS_MAX_TAPS);
@@ -297,8 +310,12 @@ TS_API int ts_ssm_scan(float* out, const float* ready, const void* proj, int pro
       if (e != cudaSuccess) TS_REFUSE((int)e, "ts_ssm_scan: shared memory %zu: %s", smem, cudaGetErrorString(e));       \
       configured = smem;                                                                                                \
     }                                                                                                                   \
-    ts_launch(ssm_scan_kernel<TT>, grid, dim3(parts * SS_COLS), smem, s, out, ready, (const TT*)proj, proj_stride, xbc_off, \
-              state, (size_t)state_stride, skip, q_start, slots, H, G, N, P, taps, parts, vec4);                        \
+    if (longest >= SS_LATE_TOKENS)                                                                                      \
+      ts_launch_late(ssm_scan_kernel<TT>, grid, dim3(parts * SS_COLS), smem, s, out, ready, (const TT*)proj, proj_stride, xbc_off, \
+                     state, (size_t)state_stride, skip, q_start, slots, H, G, N, P, taps, parts, vec4);                 \
+    else                                                                                                                \
+      ts_launch(ssm_scan_kernel<TT>, grid, dim3(parts * SS_COLS), smem, s, out, ready, (const TT*)proj, proj_stride, xbc_off, \
+                state, (size_t)state_stride, skip, q_start, slots, H, G, N, P, taps, parts, vec4);                      \
   } while (0)
   if (dtype == TS_F32) TS_SC(float);
   else if (dtype == TS_BF16) TS_SC(bf16);

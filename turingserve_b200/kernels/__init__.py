@@ -68,7 +68,7 @@ class LazyProduct:
 class CudaOps:
     """ctypes front of ``libturingserve_b200.so``."""
 
-    ABI = 13
+    ABI = 14
     UNSUPPORTED = -4            # a kernel's refusal of a shape or layout another kernel takes
 
     def __init__(self, lib_path: str) -> None:
@@ -122,7 +122,8 @@ class CudaOps:
             "ts_moe_combine": [P, P, P, P, I, I, I, I, P, P, P, P],
             "ts_hyper_norm": [P, P, P, P, I, P, P, P, P, P, F, I, I, I, I, F, I, P],
             "ts_ssm_prepare": [P, P, I, I, I, P, P, P, P, P, ctypes.c_longlong, ctypes.c_longlong, P, P, P, I, I, I, I, I, P],
-            "ts_ssm_scan": [P, P, P, I, I, P, ctypes.c_longlong, P, P, P, I, I, I, I, I, I, I, P],
+            "ts_ssm_scan": [P, P, P, I, I, P, ctypes.c_longlong, P, P, P, I, I, I, I, I, I, I, I, P],
+            "ts_lightning_ex": [P, P, I, P, P, P, P, I, I, I, I, I, I, P],
             "ts_gated_group_rmsnorm": [P, I, P, P, I, P, F, I, I, I, I, I, F, I, P],
             "ts_gate_mul": [P, I, P, I, P, I, I, I, I, F, I, P],
             "ts_act_mul": [P, P, I, I, I, I, I, P],
@@ -624,9 +625,10 @@ class CudaOps:
         """out (float32 [T, H V]): per head o_t = S_t^T q_t with S_t = decay_h S_(t-1) + k_t v_t^T, where
         q, k, v = silu of the columns [0, HD), [HD, 2HD), [2HD, 2HD + HV) of ``proj``; ``state``
         (float32 [slots, H, D, V]) is read and left updated at each request's slot."""
-        self._check(self.lib.ts_lightning(_ptr(out), _ptr(proj), proj.stride(0), _ptr(state), _ptr(decay),
-                                          _ptr(step.q_start), _ptr(step.state_slots), step.num_requests, H, D, V,
-                                          _code(proj.dtype), self._stream()), "lightning")
+        self._check(self.lib.ts_lightning_ex(_ptr(out), _ptr(proj), proj.stride(0), _ptr(state), _ptr(decay),
+                                             _ptr(step.q_start), _ptr(step.state_slots), step.num_requests, H, D, V,
+                                             int(getattr(step, "max_q_len", 0) or 0), _code(proj.dtype), self._stream()),
+                    "lightning")
 
     # -- attention with two score maps a head --------------------------------------------------------------
     def kv_write_pair(self, proj, k_off: int, v_off: int, k_cache, v_cache, slots, KVH: int, DK: int, DV: int,
@@ -899,7 +901,8 @@ class CudaOps:
         filter's last inputs (from ``proj``) included."""
         self._check(self.lib.ts_ssm_scan(_ptr(out), _ptr(ready), _ptr(proj), proj.stride(0), xbc_off, _ptr(state),
                                          state.stride(0), _ptr(skip), _ptr(step.q_start), _ptr(step.state_slots),
-                                         step.num_requests, H, G, N, P, taps, _code(proj.dtype), self._stream()), "ssm_scan")
+                                         step.num_requests, H, G, N, P, taps, int(getattr(step, "max_q_len", 0) or 0),
+                                         _code(proj.dtype), self._stream()), "ssm_scan")
 
     GATES = {"sigmoid": 0, "silu": 1}
 
