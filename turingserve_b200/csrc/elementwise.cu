@@ -431,7 +431,7 @@ __global__ void act_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, in
     const size_t t = idx / inter;
     const int i = (int)(idx - t * inter);
     const size_t gc = t * 2 * inter + gate_col(i, group);
-    out[idx] = from_f<T>(round_to<T>(ts_activate(to_f(gu[gc]), act)) * to_f(gu[gc + up_off]));
+    out[idx] = from_f<T>(round_to<T>(ts_activate_for<T>(to_f(gu[gc]), act)) * to_f(gu[gc + up_off]));
   }
 }
 
@@ -450,7 +450,7 @@ __global__ void act_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ gu
     load_vec<T, N>(gu + gc, g);
     load_vec<T, N>(gu + gc + up_off, u);
 #pragma unroll
-    for (int k = 0; k < N; ++k) o[k] = round_to<T>(ts_activate(g[k], act)) * u[k];
+    for (int k = 0; k < N; ++k) o[k] = round_to<T>(ts_activate_for<T>(g[k], act)) * u[k];
     store_vec<T, N>(out + (size_t)t * inter + i, o);
   }
 }

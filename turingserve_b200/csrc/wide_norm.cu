@@ -183,6 +183,13 @@ __device__ __forceinline__ float ts_gate(float g, int kind) {
   const float sg = 1.f / (1.f + expf(-g));
   return kind == TS_GATE_SILU ? g * sg : sg;
 }
+// On its way to a rounding to bfloat16 the hardware's approximate exponential and reciprocal serve (about 2^-21 relative,
+// against a bfloat16 step of 2^-9; see silu_for); the 32-bit type keeps the exact ones.
+template <typename T> __device__ __forceinline__ float ts_gate_for(float g, int kind) { return ts_gate(g, kind); }
+template <> __device__ __forceinline__ float ts_gate_for<bf16>(float g, int kind) {
+  const float sg = __fdividef(1.f, 1.f + __expf(-g));
+  return kind == TS_GATE_SILU ? g * sg : sg;
+}
 
 // An RMS norm over a 32-bit row in `groups` equal parts, each by its own root mean square, with a gate from a second
 // tensor that multiplies either what is normed (gate_first) or the normed result:
@@ -203,13 +210,13 @@ __global__ void gated_group_rmsnorm_kernel(T* __restrict__ out, int out_stride, 
   float ss = 0.f;
   for (int i = threadIdx.x; i < m; i += blockDim.x) {
     float v = xr[i];
-    if (gate_first) v *= ts_gate(to_f(gr[i]), gate_kind);
+    if (gate_first) v *= ts_gate_for<T>(to_f(gr[i]), gate_kind);
     ss = fmaf(v, v, ss);
   }
   ss = block_sum(ss, scratch);
   const float rstd = 1.f / sqrtf(ss / (float)m + eps);
   for (int i = threadIdx.x; i < m; i += blockDim.x) {
-    const float g = ts_gate(to_f(gr[i]), gate_kind);
+    const float g = ts_gate_for<T>(to_f(gr[i]), gate_kind);
     const float v = gate_first ? xr[i] * g * rstd * w[c0 + i] : xr[i] * rstd * w[c0 + i] * g;
     orow[i] = from_f<T>(v * scale);
   }
@@ -224,7 +231,7 @@ __global__ void gate_mul_kernel(T* __restrict__ out, int out_stride, const T* __
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / n;
     const int i = (int)(idx - t * n);
-    out[t * out_stride + i] = from_f<T>(to_f(a[t * a_stride + i]) * ts_gate(to_f(gate[t * gate_stride + i]), gate_kind) * scale);
+    out[t * out_stride + i] = from_f<T>(to_f(a[t * a_stride + i]) * ts_gate_for<T>(to_f(gate[t * gate_stride + i]), gate_kind) * scale);
   }
 }
 
@@ -348,7 +355,7 @@ __global__ void gate_mul_vec_kernel(bf16* __restrict__ out, int out_stride, cons
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const float2 af = __bfloat1622float2(ah[j]), gf = __bfloat1622float2(gh[j]);
-      oh[j] = __floats2bfloat162_rn(af.x * ts_gate(gf.x, gate_kind) * scale, af.y * ts_gate(gf.y, gate_kind) * scale);
+      oh[j] = __floats2bfloat162_rn(af.x * ts_gate_for<bf16>(gf.x, gate_kind) * scale, af.y * ts_gate_for<bf16>(gf.y, gate_kind) * scale);
     }
     *reinterpret_cast<uint4*>(out + t * out_stride + i) = ov;
   }
