@@ -996,7 +996,7 @@ def gugezen_config(z: dict, groups: int, vocab: int):
                  "rot": {"base": 500000.0, "dims": z["rot"], "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}},
         "right": {"heads": z["lheads"], "dim": z["dim"], "vdim": z["dim"],
                   "decay": [1.0 - 2.0 ** -(2 + 6 * i / max(1, z["lheads"] - 1)) for i in range(z["lheads"])]},
-        "left_scale": 0.8, "right_scale": 0.9}}
+        "left_scale": 0.7, "right_scale": 1.1}}
     ssm = {"type": "mamba2", "mixer": {"heads": z["sheads"], "vdim": z["sdim"], "state": z["state"], "groups": z["sgroups"],
                                        "conv": z["taps"], "norm_groups": z["parts"]}}
     dense = {"kind": "dense", "ff": z["ff"]}
@@ -1070,7 +1070,7 @@ def gugezen_kernels(ops, z: dict, pk: dict, T: int, B: int, ctx: int, page: int)
         step = SimpleNamespace(q_start=i32([i * per for i in range(reqs + 1)]), seq_lens=i32([seq] * reqs), num_requests=reqs,
                                num_decode=reqs if per == 1 else 0, max_q_len=per, max_seq_len=seq)
         ms = timed(lambda: ops.attention_biased(o, q, kc, vc, bt, step, G, page, D ** -0.5, 0.0, None, None, chunk=None, sinks=sinks), flush)
-        ms_g = timed(lambda: ops.gate_mul(heads, o.view(rows, H * D), gate, "sigmoid", 0.8), flush)
+        ms_g = timed(lambda: ops.gate_mul(heads, o.view(rows, H * D), gate, "sigmoid", 0.7), flush)
         seen = sum(i + 1 for i in range(seq - per, seq))
         flops = 4.0 * D * H * seen * reqs
         byts = reqs * seq * G * 2 * D * 2.0 + rows * H * D * 4.0

@@ -68,8 +68,8 @@ TINY = {
     ]), 42, 8),
     # sizes in multiples of 16 and pages of 64: heads of 64 and of 128 with values as wide (the tensor-core attention in
     # bfloat16), two copies of the stream
-    "C": (dict(width=128, vocab=300, eps=1e-6, streams=2, embedding_scale=11.3, logit_scale=0.25, layers=[
-        {**pair(4, 2, 64, 64, 0.125, (250000.0, 32, (4.0, 1.0, 4.0, 256.0)), 2, 64, 64, (0.9, 0.999), 0.8, 0.9), "mlp": dense(256)},
+    "C": (dict(width=128, vocab=300, eps=1e-6, streams=2, embedding_scale=11.3, logit_scale=0.4, layers=[
+        {**pair(4, 2, 64, 64, 0.13, (300000.0, 32, (3.0, 1.0, 3.0, 200.0)), 2, 64, 64, (0.9, 0.9995), 0.75, 1.2), "mlp": dense(256)},
         {**ssm(4, 32, 64, 1, 4, 2), "mlp": moe(8, 2, 32, 64)},
         {**pair(2, 1, 128, 128, 0.09, (10000.0, 128), 4, 32, 16, (0.6, 0.8, 0.9, 0.99), 1.0, 1.0), "mlp": moe(6, 3, 64)},
         {**ssm(4, 32, 64, 1, 4, 2), "mlp": moe(8, 2, 32, 64), "weights_of": 1},
