@@ -29,7 +29,7 @@ template <typename T>
 __global__ void __launch_bounds__(512)
 lightning_kernel(float* __restrict__ out, const T* __restrict__ proj, int proj_stride, float* __restrict__ state,
                  const float* __restrict__ decay, const int* __restrict__ q_start, const int* __restrict__ slots,
-                 int H, int D, int V, int parts, int fast_rows) {
+                 int H, int D, int V, int parts, int fast_rows, int plan) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) float smem[];
@@ -60,8 +60,62 @@ lightning_kernel(float* __restrict__ out, const T* __restrict__ proj, int proj_s
   const int raw_row = 2 * D + LT_COLS;
   const int cols_here = min(LT_COLS, V - (int)blockIdx.x * LT_COLS);
   constexpr int PER16 = 16 / (int)sizeof(T);
+  // Which pieces of a group a thread copies, and which it activates, is the same for every group: with ``plan`` (long
+  // portions) both are worked out once instead of by two divisions a piece and group.  At most LT_MAX_COPIES 16-byte
+  // copies a thread (16 rows of 2 D / PER16 + LT_COLS / PER16 pieces over 2 D threads) and LT_MAX_ACT pieces to activate.
+  constexpr int LT_MAX_COPIES = 8, LT_MAX_ACT = 4;
+  int cp_row[LT_MAX_COPIES], cp_src[LT_MAX_COPIES], cp_dst[LT_MAX_COPIES];
+  int ac_row[LT_MAX_ACT], ac_src[LT_MAX_ACT], ac_dst[LT_MAX_ACT];
+  const bool planned = plan && fast_rows;
+  if (planned) {
+    const int chunks_qk = D / PER16, chunks_v = LT_COLS / PER16, per_row = 2 * chunks_qk + chunks_v;
+#pragma unroll
+    for (int k = 0; k < LT_MAX_COPIES; ++k) {
+      const int i = threadIdx.x + k * blockDim.x;
+      cp_row[k] = LT_GROUP;                                // (beyond every group: never copied)
+      cp_src[k] = cp_dst[k] = 0;
+      if (i < LT_GROUP * per_row) {
+        const int r = i / per_row, c = i % per_row;
+        if (c < chunks_qk) {
+          cp_row[k] = r;
+          cp_src[k] = r * proj_stride + q_off + c * PER16;
+          cp_dst[k] = r * raw_row + c * PER16;
+        } else if (c < 2 * chunks_qk) {
+          cp_row[k] = r;
+          cp_src[k] = r * proj_stride + k_off + (c - chunks_qk) * PER16;
+          cp_dst[k] = r * raw_row + D + (c - chunks_qk) * PER16;
+        } else if ((c - 2 * chunks_qk) * PER16 < cols_here) {
+          cp_row[k] = r;
+          cp_src[k] = r * proj_stride + v_off + blockIdx.x * LT_COLS + (c - 2 * chunks_qk) * PER16;
+          cp_dst[k] = r * raw_row + 2 * D + (c - 2 * chunks_qk) * PER16;
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < LT_MAX_ACT; ++k) {
+      const int i = threadIdx.x + k * blockDim.x;
+      ac_row[k] = LT_GROUP;
+      ac_src[k] = ac_dst[k] = 0;
+      if (i < LT_GROUP * 2 * chunks_qk) {
+        const int r = i / (2 * chunks_qk), c = i % (2 * chunks_qk);
+        const int which = c >= chunks_qk, cc = (which ? c - chunks_qk : c) * PER16;
+        ac_row[k] = r;
+        ac_src[k] = r * raw_row + which * D + cc;
+        ac_dst[k] = which * LT_GROUP * Dp + r * Dp + cc;   // (k_s lies LT_GROUP * Dp behind q_s)
+      }
+    }
+  }
   auto fetch = [&](int g0, int buf) {
     if (!fast_rows) return;
+    if (planned) {
+      const int gn = min(LT_GROUP, n - g0);
+      const T* first = proj + (size_t)(t0 + g0) * proj_stride;
+      T* dst0 = raw + (size_t)buf * LT_GROUP * raw_row;
+#pragma unroll
+      for (int k = 0; k < LT_MAX_COPIES; ++k)
+        if (cp_row[k] < gn) cp_async_16(dst0 + cp_dst[k], first + cp_src[k], true);
+      return;
+    }
     const int gn = min(LT_GROUP, n - g0);
     const int chunks_qk = D / PER16, chunks_v = LT_COLS / PER16, per_row = 2 * chunks_qk + chunks_v;
     for (int i = threadIdx.x; i < gn * per_row; i += blockDim.x) {
@@ -87,7 +141,19 @@ lightning_kernel(float* __restrict__ out, const T* __restrict__ proj, int proj_s
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();                                       // this group's raw rows are here; the group before is stored
-    if (fast_rows) {
+    if (planned) {
+      const T* raw0 = raw + (size_t)buf * LT_GROUP * raw_row;
+#pragma unroll
+      for (int k = 0; k < LT_MAX_ACT; ++k) {
+        if (ac_row[k] < gn) {
+          const uint4 rawv = *reinterpret_cast<const uint4*>(raw0 + ac_src[k]);
+          const T* e = reinterpret_cast<const T*>(&rawv);
+          float* dst = q_s + ac_dst[k];
+#pragma unroll
+          for (int u = 0; u < PER16; ++u) dst[u] = act_silu<T>(to_f(e[u]));
+        }
+      }
+    } else if (fast_rows) {
       // 16 bytes (PER16 values) of q or k at a time: the index arithmetic once a piece, not once a value
       const int chunks = D / PER16;
       for (int i = threadIdx.x; i < gn * 2 * chunks; i += blockDim.x) {
@@ -118,6 +184,7 @@ lightning_kernel(float* __restrict__ out, const T* __restrict__ proj, int proj_s
       v_s[i] = vv;
     }
     __syncthreads();
+#pragma unroll 2
     for (int r = 0; r < gn; ++r) {
       const float vj = v_s[r * LT_COLS + col];
       const float4* qr = reinterpret_cast<const float4*>(q_s + r * Dp + part * LT_ROWS);
@@ -198,10 +265,10 @@ TS_API int ts_lightning_ex(float* out, const void* proj, int proj_stride, float*
     }                                                                                                               \
     if (longest >= LT_LATE_TOKENS)                                                                                  \
       ts_launch_late(lightning_kernel<TT>, dim3(grid), dim3(parts * LT_COLS), smem, s, out, (const TT*)proj, proj_stride, \
-                     state, decay, q_start, slots, H, D, V, parts, fast_rows);                                      \
+                     state, decay, q_start, slots, H, D, V, parts, fast_rows, 1);                                   \
     else                                                                                                            \
       ts_launch(lightning_kernel<TT>, dim3(grid), dim3(parts * LT_COLS), smem, s, out, (const TT*)proj, proj_stride, \
-                state, decay, q_start, slots, H, D, V, parts, fast_rows);                                           \
+                state, decay, q_start, slots, H, D, V, parts, fast_rows, 0);                                        \
   } while (0)
   if (dtype == TS_F32) TS_LT(float);
   else if (dtype == TS_BF16) TS_LT(bf16);

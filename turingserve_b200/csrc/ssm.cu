@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(512)
 ssm_scan_kernel(float* __restrict__ out, const float* __restrict__ ready, const T* __restrict__ proj, int proj_stride,
                 int xbc_off, float* __restrict__ state, size_t state_stride, const float* __restrict__ skip,
                 const int* __restrict__ q_start, const int* __restrict__ slots, int H, int G, int N, int P, int taps,
-                int parts, int vec4) {
+                int parts, int vec4, int plan) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) float smem[];
@@ -145,13 +145,47 @@ ssm_scan_kernel(float* __restrict__ out, const float* __restrict__ ready, const 
   for (int i = threadIdx.x; i < 2 * stage; i += blockDim.x) smem[i] = 0.f;     // (what no copy writes stays zero)
   __syncthreads();
 
+  // Which pieces of a group a thread copies is the same for every group: with ``plan`` (long portions) it is worked out
+  // once (the divisions of the index by the pieces a row would otherwise cost more instructions a group than the copies
+  // themselves; for a single token the plan itself is what costs: 28.7 -> 36.9 us).  16-byte pieces: at most
+  // SS_MAX_COPIES a thread (16 rows of N / 2 + 4 pieces over 16 ceil(N / 8) threads).
+  constexpr int SS_MAX_COPIES = 8;
+  int cp_row[SS_MAX_COPIES], cp_src[SS_MAX_COPIES], cp_dst[SS_MAX_COPIES];
+  if (vec4 && plan) {
+    const int nb = N / 4, nx = cols_here / 4, per_row = 2 * nb + nx;
+#pragma unroll
+    for (int k = 0; k < SS_MAX_COPIES; ++k) {
+      const int i = threadIdx.x + k * blockDim.x;
+      cp_row[k] = SS_GROUP;                                // (beyond every group: never copied)
+      cp_src[k] = cp_dst[k] = 0;
+      if (i < SS_GROUP * per_row) {
+        const int r = i / per_row, c = i % per_row;
+        cp_row[k] = r;
+        if (c < nb) {
+          cp_src[k] = r * W + inner + g * N + 4 * c;
+          cp_dst[k] = r * Np + 4 * c;
+        } else if (c < 2 * nb) {
+          cp_src[k] = r * W + inner + GN + g * N + 4 * (c - nb);
+          cp_dst[k] = SS_GROUP * Np + r * Np + 4 * (c - nb);
+        } else {
+          cp_src[k] = r * W + h * P + blockIdx.x * SS_COLS + 4 * (c - 2 * nb);
+          cp_dst[k] = 2 * SS_GROUP * Np + r * SS_COLS + 4 * (c - 2 * nb);
+        }
+      }
+    }
+  }
   auto fetch = [&](int g0, int buf) {
     const int gn = min(SS_GROUP, n - g0);
     float* Bs = smem + (size_t)buf * stage;
     float* Cs = Bs + SS_GROUP * Np;
     float* xs = Cs + SS_GROUP * Np;
     float* da = xs + SS_GROUP * SS_COLS;
-    if (vec4) {
+    if (vec4 && plan) {
+      const float* first = ready + (size_t)(t0 + g0) * W;
+#pragma unroll
+      for (int k = 0; k < SS_MAX_COPIES; ++k)
+        if (cp_row[k] < gn) cp_async_16(Bs + cp_dst[k], first + cp_src[k], true);
+    } else if (vec4) {
       const int nb = N / 4, nx = cols_here / 4, per_row = 2 * nb + nx;
       for (int i = threadIdx.x; i < gn * per_row; i += blockDim.x) {
         const int r = i / per_row, c = i % per_row;
@@ -190,6 +224,7 @@ ssm_scan_kernel(float* __restrict__ out, const float* __restrict__ ready, const 
     const float* Cs = Bs + SS_GROUP * Np;
     const float* xs = Cs + SS_GROUP * Np;
     const float* da = xs + SS_GROUP * SS_COLS;
+#pragma unroll 2
     for (int r = 0; r < gn; ++r) {
       const float dt = da[2 * r], a = da[2 * r + 1];
       const float xv = xs[r * SS_COLS + col];
@@ -312,10 +347,10 @@ TS_API int ts_ssm_scan(float* out, const float* ready, const void* proj, int pro
     }                                                                                                                   \
     if (longest >= SS_LATE_TOKENS)                                                                                      \
       ts_launch_late(ssm_scan_kernel<TT>, grid, dim3(parts * SS_COLS), smem, s, out, ready, (const TT*)proj, proj_stride, xbc_off, \
-                     state, (size_t)state_stride, skip, q_start, slots, H, G, N, P, taps, parts, vec4);                 \
+                     state, (size_t)state_stride, skip, q_start, slots, H, G, N, P, taps, parts, vec4, 1);              \
     else                                                                                                                \
       ts_launch(ssm_scan_kernel<TT>, grid, dim3(parts * SS_COLS), smem, s, out, ready, (const TT*)proj, proj_stride, xbc_off, \
-                state, (size_t)state_stride, skip, q_start, slots, H, G, N, P, taps, parts, vec4);                      \
+                state, (size_t)state_stride, skip, q_start, slots, H, G, N, P, taps, parts, vec4, 0);                   \
   } while (0)
   if (dtype == TS_F32) TS_SC(float);
   else if (dtype == TS_BF16) TS_SC(bf16);
