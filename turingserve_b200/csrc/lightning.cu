@@ -25,11 +25,13 @@ constexpr int LT_ROWS = 8;       // state rows per thread (registers)
 
 template <typename T> __device__ __forceinline__ float act_silu(float z) { return round_to<T>(silu_for<T>(z)); }
 
-template <typename T>
+// PLAN: an instance of its own for long portions (its per-thread plan of copies and activations costs 60 registers more,
+// which would halve the blocks an SM holds in single-token steps)
+template <typename T, bool PLAN>
 __global__ void __launch_bounds__(512)
 lightning_kernel(float* __restrict__ out, const T* __restrict__ proj, int proj_stride, float* __restrict__ state,
                  const float* __restrict__ decay, const int* __restrict__ q_start, const int* __restrict__ slots,
-                 int H, int D, int V, int parts, int fast_rows, int plan) {
+                 int H, int D, int V, int parts, int fast_rows) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) float smem[];
@@ -60,13 +62,13 @@ lightning_kernel(float* __restrict__ out, const T* __restrict__ proj, int proj_s
   const int raw_row = 2 * D + LT_COLS;
   const int cols_here = min(LT_COLS, V - (int)blockIdx.x * LT_COLS);
   constexpr int PER16 = 16 / (int)sizeof(T);
-  // Which pieces of a group a thread copies, and which it activates, is the same for every group: with ``plan`` (long
+  // Which pieces of a group a thread copies, and which it activates, is the same for every group: with PLAN (long
   // portions) both are worked out once instead of by two divisions a piece and group.  At most LT_MAX_COPIES 16-byte
   // copies a thread (16 rows of 2 D / PER16 + LT_COLS / PER16 pieces over 2 D threads) and LT_MAX_ACT pieces to activate.
   constexpr int LT_MAX_COPIES = 8, LT_MAX_ACT = 4;
   int cp_row[LT_MAX_COPIES], cp_src[LT_MAX_COPIES], cp_dst[LT_MAX_COPIES];
   int ac_row[LT_MAX_ACT], ac_src[LT_MAX_ACT], ac_dst[LT_MAX_ACT];
-  const bool planned = plan && fast_rows;
+  const bool planned = PLAN && fast_rows;
   if (planned) {
     const int chunks_qk = D / PER16, chunks_v = LT_COLS / PER16, per_row = 2 * chunks_qk + chunks_v;
 #pragma unroll
@@ -259,16 +261,18 @@ TS_API int ts_lightning_ex(float* out, const void* proj, int proj_stride, float*
   do {                                                                                                              \
     static size_t configured = 0;                                                                                   \
     if (smem > 48 * 1024 && smem > configured) {                                                                    \
-      cudaError_t e = cudaFuncSetAttribute(lightning_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      cudaError_t e = cudaFuncSetAttribute(lightning_kernel<TT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e == cudaSuccess)                                                                                         \
+        e = cudaFuncSetAttribute(lightning_kernel<TT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
       if (e != cudaSuccess) TS_REFUSE((int)e, "ts_lightning: shared memory %zu: %s", smem, cudaGetErrorString(e)); \
       configured = smem;                                                                                            \
     }                                                                                                               \
     if (longest >= LT_LATE_TOKENS)                                                                                  \
-      ts_launch_late(lightning_kernel<TT>, dim3(grid), dim3(parts * LT_COLS), smem, s, out, (const TT*)proj, proj_stride, \
-                     state, decay, q_start, slots, H, D, V, parts, fast_rows, 1);                                   \
+      ts_launch_late(lightning_kernel<TT, true>, dim3(grid), dim3(parts * LT_COLS), smem, s, out, (const TT*)proj, proj_stride, \
+                     state, decay, q_start, slots, H, D, V, parts, fast_rows);                                      \
     else                                                                                                            \
-      ts_launch(lightning_kernel<TT>, dim3(grid), dim3(parts * LT_COLS), smem, s, out, (const TT*)proj, proj_stride, \
-                state, decay, q_start, slots, H, D, V, parts, fast_rows, 0);                                        \
+      ts_launch(lightning_kernel<TT, false>, dim3(grid), dim3(parts * LT_COLS), smem, s, out, (const TT*)proj, proj_stride, \
+                state, decay, q_start, slots, H, D, V, parts, fast_rows);                                           \
   } while (0)
   if (dtype == TS_F32) TS_LT(float);
   else if (dtype == TS_BF16) TS_LT(bf16);

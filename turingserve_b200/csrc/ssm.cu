@@ -112,12 +112,14 @@ ssm_prepare_kernel(float* __restrict__ ready, const T* __restrict__ proj, int pr
   }
 }
 
-template <typename T>
+// PLAN: an instance of its own for long portions (its per-thread copy plan costs 60 registers more, which would halve the
+// blocks an SM holds in single-token steps: 51 -> 59 us at 112 heads)
+template <typename T, bool PLAN>
 __global__ void __launch_bounds__(512)
 ssm_scan_kernel(float* __restrict__ out, const float* __restrict__ ready, const T* __restrict__ proj, int proj_stride,
                 int xbc_off, float* __restrict__ state, size_t state_stride, const float* __restrict__ skip,
                 const int* __restrict__ q_start, const int* __restrict__ slots, int H, int G, int N, int P, int taps,
-                int parts, int vec4, int plan) {
+                int parts, int vec4) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) float smem[];
@@ -145,13 +147,13 @@ ssm_scan_kernel(float* __restrict__ out, const float* __restrict__ ready, const 
   for (int i = threadIdx.x; i < 2 * stage; i += blockDim.x) smem[i] = 0.f;     // (what no copy writes stays zero)
   __syncthreads();
 
-  // Which pieces of a group a thread copies is the same for every group: with ``plan`` (long portions) it is worked out
+  // Which pieces of a group a thread copies is the same for every group: with PLAN (long portions) it is worked out
   // once (the divisions of the index by the pieces a row would otherwise cost more instructions a group than the copies
   // themselves; for a single token the plan itself is what costs: 28.7 -> 36.9 us).  16-byte pieces: at most
   // SS_MAX_COPIES a thread (16 rows of N / 2 + 4 pieces over 16 ceil(N / 8) threads).
   constexpr int SS_MAX_COPIES = 8;
   int cp_row[SS_MAX_COPIES], cp_src[SS_MAX_COPIES], cp_dst[SS_MAX_COPIES];
-  if (vec4 && plan) {
+  if (PLAN && vec4) {
     const int nb = N / 4, nx = cols_here / 4, per_row = 2 * nb + nx;
 #pragma unroll
     for (int k = 0; k < SS_MAX_COPIES; ++k) {
@@ -180,7 +182,7 @@ ssm_scan_kernel(float* __restrict__ out, const float* __restrict__ ready, const 
     float* Cs = Bs + SS_GROUP * Np;
     float* xs = Cs + SS_GROUP * Np;
     float* da = xs + SS_GROUP * SS_COLS;
-    if (vec4 && plan) {
+    if (PLAN && vec4) {
       const float* first = ready + (size_t)(t0 + g0) * W;
 #pragma unroll
       for (int k = 0; k < SS_MAX_COPIES; ++k)
@@ -341,16 +343,18 @@ TS_API int ts_ssm_scan(float* out, const float* ready, const void* proj, int pro
   do {                                                                                                                  \
     static size_t configured = 0;                                                                                       \
     if (smem > 48 * 1024 && smem > configured) {                                                                        \
-      cudaError_t e = cudaFuncSetAttribute(ssm_scan_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      cudaError_t e = cudaFuncSetAttribute(ssm_scan_kernel<TT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e == cudaSuccess)                                                                                             \
+        e = cudaFuncSetAttribute(ssm_scan_kernel<TT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
       if (e != cudaSuccess) TS_REFUSE((int)e, "ts_ssm_scan: shared memory %zu: %s", smem, cudaGetErrorString(e));       \
       configured = smem;                                                                                                \
     }                                                                                                                   \
     if (longest >= SS_LATE_TOKENS)                                                                                      \
-      ts_launch_late(ssm_scan_kernel<TT>, grid, dim3(parts * SS_COLS), smem, s, out, ready, (const TT*)proj, proj_stride, xbc_off, \
-                     state, (size_t)state_stride, skip, q_start, slots, H, G, N, P, taps, parts, vec4, 1);              \
+      ts_launch_late(ssm_scan_kernel<TT, true>, grid, dim3(parts * SS_COLS), smem, s, out, ready, (const TT*)proj, proj_stride, xbc_off, \
+                     state, (size_t)state_stride, skip, q_start, slots, H, G, N, P, taps, parts, vec4);                 \
     else                                                                                                                \
-      ts_launch(ssm_scan_kernel<TT>, grid, dim3(parts * SS_COLS), smem, s, out, ready, (const TT*)proj, proj_stride, xbc_off, \
-                state, (size_t)state_stride, skip, q_start, slots, H, G, N, P, taps, parts, vec4, 0);                   \
+      ts_launch(ssm_scan_kernel<TT, false>, grid, dim3(parts * SS_COLS), smem, s, out, ready, (const TT*)proj, proj_stride, xbc_off, \
+                state, (size_t)state_stride, skip, q_start, slots, H, G, N, P, taps, parts, vec4);                      \
   } while (0)
   if (dtype == TS_F32) TS_SC(float);
   else if (dtype == TS_BF16) TS_SC(bf16);
