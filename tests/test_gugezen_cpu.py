@@ -242,3 +242,26 @@ def test_the_plain_functions_agree_with_closed_forms():
     _, after1 = plain.forward({k: v for k, v in cfg.items() if k != "streams"}, one, [1, 3, 2])
     x0 = W["embed"].double()[torch.tensor([1, 3, 2])]
     assert torch.allclose(after2[0], after1[0] + x0)             # copy 1 keeps the embedding; the sum holds both
+
+
+def test_a_pair_takes_one_cache_and_one_state_and_mixers_that_expose_their_products():
+    from turingserve_b200.parts.base import BuildContext, build
+    ctx = BuildContext(hidden_size=24, dtype=torch.float32, device=torch.device("cpu"), max_positions=16)
+    lin = LightningSpec(num_heads=2, key_dim=4, value_dim=6, decays=(0.5, 0.9), norm_eps=1e-6)
+    att = SinkAttentionSpec(num_heads=2, num_kv_heads=1, key_dim=8, value_dim=4, scale=0.3, qkv_bias=True, out_gate=True)
+    pair = build("mixer", PairedMixerSpec(left=att, right=lin, left_scale=0.5, right_scale=2.0), ctx)
+    assert pair.cache_need() == CacheNeed(1, 8, None, value_dim=4, chunk=None) and pair.state_need() == StateNeed((2, 4, 6), torch.float32)
+    names = set(pair.parameters())
+    assert {"left.q", "left.q.b", "left.g", "left.sink", "right.norm", "right.o"} <= names and len(names) == 9 + 6
+    # either order of the halves
+    assert build("mixer", PairedMixerSpec(left=lin, right=att), ctx).cache_need() is not None
+    with pytest.raises(ValueError, match="at most one"):
+        build("mixer", PairedMixerSpec(left=lin, right=lin), ctx)
+    with pytest.raises(ValueError, match="at most one"):
+        build("mixer", PairedMixerSpec(left=att, right=att), ctx)
+    # a mixer that does not expose its products is refused when the pair is loaded, by name
+    ssm = Mamba2Spec(num_heads=2, head_dim=4, state_size=4, num_groups=1, conv_taps=2, norm_groups=1, norm_eps=1e-6)
+    odd = build("mixer", PairedMixerSpec(left=att, right=ssm), ctx)
+    tensors = {n: torch.zeros(p.shape) for n, p in odd.parameters().items()}
+    with pytest.raises(NotImplementedError, match="Mamba2 does not expose"):
+        odd.load(tensors)
